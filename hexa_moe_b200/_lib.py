@@ -1,0 +1,90 @@
+"""ctypes binding of libhexa_moe_b200.so (the C ABI declared in include/hexa_moe_b200.h).
+
+The library is the only execution path: there is no CPU or PyTorch fallback.  `lib()` raises
+if the shared object is missing; every wrapper raises `HexaError` on a non-zero status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libhexa_moe_b200.so")
+
+F32, F16, BF16 = 0, 1, 2
+ACT_NONE, ACT_RELU, ACT_GELU, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3, 4
+B_NK, B_KN = 0, 1
+EPI_LINEAR, EPI_ACT, EPI_DACT = 0, 1, 2
+ENGINE_AUTO, ENGINE_TCGEN05, ENGINE_SIMT = 0, 1, 2
+ROW_TILE = 128
+
+_DT = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+i32p, vp, i64, ci, sz = C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/hexa_moe_b200.h one to one
+SIGNATURES = {
+    "hexa_version": (ci, []),
+    "hexa_last_error_string": (C.c_char_p, []),
+    "hexa_set_status_word": (ci, [vp]),
+    "hexa_route_row_capacity": (i64, [i64, ci, ci, ci]),
+    "hexa_route_workspace_bytes": (sz, [i64, ci, ci]),
+    "hexa_route": (ci, [vp, i64, ci, i64, i64, ci, ci, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
+    "hexa_gather_rows": (ci, [vp, i64, vp, vp, ci, i64, i64, vp, i64, ci, vp]),
+    "hexa_combine_rows": (ci, [vp, i64, vp, i64, ci, i64, vp, i64, ci, vp]),
+    "hexa_esmm": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, vp, i64, vp, i64, vp, vp, vp, ci, i64, i64, i64, ci, ci, ci, ci, vp]),
+    "hexa_estmm": (ci, [vp, i64, vp, i64, vp, ci, i64, i64, i64, vp, i64, i64, ci, ci, ci, ci, vp]),
+    "hexa_ess_workspace_bytes": (sz, [i64, i64]),
+    "hexa_ess": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, ci, vp, sz, vp]),
+    "hexa_mask_pad_rows": (ci, [vp, i64, vp, vp, ci, i64, i64, ci, vp]),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+class HexaError(RuntimeError):
+    pass
+
+
+def lib():
+    """Load the shared library once.  Fails loudly if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise HexaError(
+                        f"{LIB_PATH} is missing: build it with `python -m hexa_moe_b200.build` "
+                        "(there is no fallback path)")
+                handle = C.CDLL(LIB_PATH)
+                for name, (res, args) in SIGNATURES.items():
+                    fn = getattr(handle, name)      # AttributeError if the symbol is not exported
+                    fn.restype, fn.argtypes = res, args
+                _lib = handle
+    return _lib
+
+
+def check(status: int, what: str):
+    if status != 0:
+        raise HexaError(f"{what} failed ({status}): {lib().hexa_last_error_string().decode()}")
+
+
+def dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise HexaError(f"unsupported dtype {t.dtype}")
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def stream_of(t: torch.Tensor) -> int:
+    if not t.is_cuda:
+        raise HexaError("hexa_moe_b200 operators run on CUDA tensors only (no CPU path)")
+    return torch.cuda.current_stream(t.device).cuda_stream

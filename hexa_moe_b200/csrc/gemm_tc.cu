@@ -1,0 +1,623 @@
+// tcgen05 / TMEM / TMA grouped GEMMs on the sorted-row layout (sm_100a only):
+//   ESMM   c[r,:]  = a[r,:] x b[expert(r)]   (b K-major "NK" or N-major "KN"), fused bias / activation /
+//                    activation-derivative epilogue, pad rows written as zeros
+//   ESTMM  out[e]  = p_e^T x q_e             (contraction over the expert's ragged row segment; both
+//                    operands are MN-major in shared memory, no transposed copy is ever made)
+//
+// One persistent CTA per SM walks a static tile list (tile = blockIdx.x + i*gridDim.x).  Warp roles:
+//   warp 0      TMA producer: 128B-swizzled tiles of A and B into a kStages-deep shared-memory ring
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
+//               accumulators, tcgen05.commit releases ring slots and publishes finished accumulators
+//   warps 2..9  epilogue: tcgen05.ld of the accumulator (lane quadrant = warp % 4, two warps per
+//               quadrant split the columns), fused epilogue math, 16-byte global stores
+// so the epilogue of tile i overlaps the MMAs of tile i+1.  Every mbarrier wait is bounded: after
+// ~2 s a CTA raises an abort flag, records a code in the status word and drains.
+//
+// Segments are aligned to 128 rows, so an ESMM tile never straddles two experts and an ESTMM
+// k-block (64 rows) never reads another expert's rows; pad rows hold zeros and add nothing.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <stdlib.h>
+
+#include "hexa_common.cuh"
+
+namespace hexa {
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;   // one 128-byte swizzle span of 16-bit elements
+constexpr int UMMA_K = 16;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 32 * (2 + kEpiWarps);
+constexpr uint32_t kABytes = BLOCK_M * BLOCK_K * 2;  // 16 KB
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+enum Mode { ESMM_NK = 0, ESMM_KN = 1, ESTMM = 2 };
+
+struct Params {
+  const int32_t* tile_expert;
+  const int32_t* pad_offsets;
+  const int32_t* row_token;
+  const float* bias;
+  int64_t ldbias;
+  void* aux;
+  int64_t ldaux;
+  void* c;          // ESMM: c ; ESTMM: out
+  int64_t ldc;
+  int64_t c_estride;  // ESTMM only
+  int64_t n;        // output columns
+  int64_t k;        // ESMM: contraction length ; ESTMM: unused
+  int64_t m;        // ESTMM: output rows per expert
+  int E;
+  int epilogue, act;
+  int is_bf16;      // 16-bit flavour of the inputs (and of 16-bit outputs)
+  int out_f32;      // ESTMM: fp32 output
+  int beta;         // ESTMM: accumulate into out
+  int mn_swap;      // debug: swap LBO/SBO of MN-major descriptors
+  int32_t* status;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false when this CTA is aborting (its own limit ran out or another role's did).
+__device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int code) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0xFF) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tm, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+// bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+// [46,48) version, [61,64) layout type (2 = SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, int is_bf16) {
+  if (is_bf16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float unpack_lo(uint32_t w, int is_bf16) {
+  if (is_bf16) return __uint_as_float(w << 16);
+  return __half2float(__ushort_as_half((unsigned short)(w & 0xFFFFu)));
+}
+__device__ __forceinline__ float unpack_hi(uint32_t w, int is_bf16) {
+  if (is_bf16) return __uint_as_float(w & 0xFFFF0000u);
+  return __half2float(__ushort_as_half((unsigned short)(w >> 16)));
+}
+
+template <int BN> struct Cfg {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr uint32_t kBBytes = BN * BLOCK_K * 2;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators; 256 or 512, a power of two
+  static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + 256 /*barriers*/;
+};
+
+struct Tile {
+  int e;          // expert
+  int row0;       // ESMM: first sorted row of the tile ; ESTMM: first row of the expert's segment
+  int col0;       // first output column
+  int m0;         // ESTMM: first output row
+  int num_kb;     // k-blocks to accumulate
+};
+
+template <int BN, int MODE>
+__device__ __forceinline__ bool get_tile(const Params& p, int64_t t, Tile& tile) {
+  if (MODE == ESTMM) {
+    const int64_t MT = (p.m + BLOCK_M - 1) / BLOCK_M, NT = (p.n + BN - 1) / BN;
+    if (t >= (int64_t)p.E * MT * NT) return false;
+    const int e = (int)(t / (MT * NT));
+    const int64_t rem = t - (int64_t)e * MT * NT;
+    tile.e = e;
+    tile.m0 = (int)(rem / NT) * BLOCK_M;
+    tile.col0 = (int)(rem % NT) * BN;
+    tile.row0 = p.pad_offsets[e];
+    tile.num_kb = (p.pad_offsets[e + 1] - tile.row0) / BLOCK_K;
+    return true;
+  } else {
+    const int64_t NT = (p.n + BN - 1) / BN;
+    const int64_t mblocks = p.pad_offsets[p.E] / BLOCK_M;
+    if (t >= mblocks * NT) return false;
+    const int64_t mb = t / NT;
+    tile.e = p.tile_expert[mb];
+    tile.row0 = (int)(mb * BLOCK_M);
+    tile.col0 = (int)(t % NT) * BN;
+    tile.m0 = 0;
+    tile.num_kb = (int)((p.k + BLOCK_K - 1) / BLOCK_K);
+    return tile.e >= 0;
+  }
+}
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  using C = Cfg<BN>;
+  constexpr int kStages = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * C::kStageBytes);
+  uint64_t* full = bars;                  // [kStages]  producer -> MMA
+  uint64_t* empty = bars + kStages;       // [kStages]  MMA -> producer
+  uint64_t* acc_full = bars + 2 * kStages;        // [2] MMA -> epilogue
+  uint64_t* acc_empty = bars + 2 * kStages + 2;   // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], kEpiWarps); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // the allocating warp also frees
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      Tile tile;
+      for (int64_t t = blockIdx.x; ok && get_tile<BN, MODE>(p, t, tile); t += gridDim.x) {
+        for (int kb = 0; kb < tile.num_kb; ++kb) {
+          if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, 1))) break;
+          uint8_t* sA = smem + (size_t)stage * C::kStageBytes;
+          uint8_t* sB = sA + kABytes;
+          mbar_expect_tx(&full[stage], C::kStageBytes);
+          if (MODE == ESTMM) {
+            const int r = tile.row0 + kb * BLOCK_K;
+#pragma unroll
+            for (int c = 0; c < BLOCK_M / 64; ++c) tma_load_2d(sA + c * 8192, &tmA, &full[stage], tile.m0 + c * 64, r);
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sB + c * 8192, &tmB, &full[stage], tile.col0 + c * 64, r);
+          } else {
+            tma_load_2d(sA, &tmA, &full[stage], kb * BLOCK_K, tile.row0);
+            if (MODE == ESMM_NK) {
+              tma_load_3d(sB, &tmB, &full[stage], kb * BLOCK_K, tile.col0, tile.e);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BN / 64; ++c)
+                tma_load_3d(sB + c * 8192, &tmB, &full[stage], tile.col0 + c * 64, kb * BLOCK_K, tile.e);
+            }
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr bool kAMn = (MODE == ESTMM), kBMn = (MODE != ESMM_NK);
+      // instruction descriptor: fp32 accumulate, A/B format (0 = f16, 1 = bf16), majors, N>>3, M>>4
+      const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((kAMn ? 1u : 0u) << 15) | ((kBMn ? 1u : 0u) << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+      // K-major: 8-row groups 1024 B apart (SBO), LBO unused (1).  MN-major: 64-element column chunks
+      // BLOCK_K*128 B apart (LBO), 8-k groups 1024 B apart (SBO).
+      uint32_t mn_lbo = BLOCK_K * 128, mn_sbo = 1024;
+      if (p.mn_swap) { uint32_t x = mn_lbo; mn_lbo = mn_sbo; mn_sbo = x; }
+      const uint32_t a_lbo = kAMn ? mn_lbo : 16, a_sbo = kAMn ? mn_sbo : 1024;
+      const uint32_t b_lbo = kBMn ? mn_lbo : 16, b_sbo = kBMn ? mn_sbo : 1024;
+      // start-address advance per K=16 step, in 16-byte units: 32 B inside the swizzle row (K-major)
+      // or two 8-k groups = 2048 B (MN-major)
+      const uint32_t a_step = kAMn ? (2048u >> 4) : (32u >> 4);
+      const uint32_t b_step = kBMn ? (2048u >> 4) : (32u >> 4);
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      Tile tile;
+      int it = 0;
+      for (int64_t t = blockIdx.x; ok && get_tile<BN, MODE>(p, t, tile); t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, 2))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < tile.num_kb; ++kb) {
+          if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status, 3))) break;
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + (size_t)stage * C::kStageBytes);
+          const uint64_t adesc = make_smem_desc(sA, a_lbo, a_sbo);
+          const uint64_t bdesc = make_smem_desc(sA + kABytes, b_lbo, b_sbo);
+#pragma unroll
+          for (int j = 0; j < BLOCK_K / UMMA_K; ++j)
+            umma_f16(d_tmem, adesc + (uint64_t)(j * a_step), bdesc + (uint64_t)(j * b_step), idesc, (kb | j) != 0 ? 1u : 0u);
+          umma_commit(&empty[stage]);  // slot reusable once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        if (tile.num_kb > 0) umma_commit(&acc_full[acc]);
+        else mbar_arrive(&acc_full[acc]);  // empty segment: nothing to wait for, epilogue writes zeros
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;       // which half of the BN columns
+    const int is_bf16 = p.is_bf16;
+    bool ok = true;
+    Tile tile;
+    int it = 0;
+    for (int64_t t = blockIdx.x; ok && get_tile<BN, MODE>(p, t, tile); t += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      if (!(ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4))) break;
+      tc_fence_after();
+      const int rloc = q * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int cc = 0; cc < BN / 2 / 32; ++cc) {
+        const int cloc = half * (BN / 2) + cc * 32;
+        const int64_t gcol = (int64_t)tile.col0 + cloc;
+        if (gcol >= p.n) break;  // uniform across the warp
+        uint32_t v[32];
+        if (tile.num_kb > 0) {
+          tmem_ld32(t_row + (uint32_t)cloc, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (MODE == ESTMM) {
+          const int64_t mrow = (int64_t)tile.m0 + rloc;
+          if (mrow < p.m) {
+            if (p.out_f32) {
+              float* o = reinterpret_cast<float*>(p.c) + (int64_t)tile.e * p.c_estride + mrow * p.ldc + gcol;
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                if (gcol + g * 4 < p.n) {
+                  float4 w = make_float4(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1]),
+                                         __uint_as_float(v[4 * g + 2]), __uint_as_float(v[4 * g + 3]));
+                  if (p.beta) {
+                    float4 old = *reinterpret_cast<float4*>(o + g * 4);
+                    w.x += old.x; w.y += old.y; w.z += old.z; w.w += old.w;
+                  }
+                  *reinterpret_cast<float4*>(o + g * 4) = w;
+                }
+              }
+            } else {
+              uint16_t* o = reinterpret_cast<uint16_t*>(p.c) + (int64_t)tile.e * p.c_estride + mrow * p.ldc + gcol;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (gcol + g * 8 < p.n) {
+                  uint4 w;
+                  uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
+                  if (p.beta) {
+                    uint4 old = *reinterpret_cast<uint4*>(o + g * 8);
+                    const uint32_t* op = reinterpret_cast<const uint32_t*>(&old);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                      wp[i] = pack2(__uint_as_float(v[8 * g + 2 * i]) + unpack_lo(op[i], is_bf16),
+                                    __uint_as_float(v[8 * g + 2 * i + 1]) + unpack_hi(op[i], is_bf16), is_bf16);
+                  } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                      wp[i] = pack2(__uint_as_float(v[8 * g + 2 * i]), __uint_as_float(v[8 * g + 2 * i + 1]), is_bf16);
+                  }
+                  *reinterpret_cast<uint4*>(o + g * 8) = w;
+                }
+              }
+            }
+          }
+        } else {
+          const int64_t r = (int64_t)tile.row0 + rloc;
+          const bool live = p.row_token == nullptr || p.row_token[r] >= 0;
+          float f[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+          if (p.bias) {
+            const float* bp = p.bias + (int64_t)tile.e * p.ldbias + gcol;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (gcol + g * 4 < p.n) {
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(bp + g * 4));
+                f[4 * g] += bv.x; f[4 * g + 1] += bv.y; f[4 * g + 2] += bv.z; f[4 * g + 3] += bv.w;
+              }
+            }
+          }
+          uint16_t* cp = reinterpret_cast<uint16_t*>(p.c) + r * p.ldc + gcol;
+          uint16_t* xp = p.aux ? reinterpret_cast<uint16_t*>(p.aux) + r * p.ldaux + gcol : nullptr;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (gcol + g * 8 >= p.n) break;
+            uint4 w;
+            uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
+            if (p.epilogue == HEXA_EPI_ACT) {
+              if (xp) {
+                uint4 y;
+                uint32_t* yp = reinterpret_cast<uint32_t*>(&y);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) yp[i] = live ? pack2(f[8 * g + 2 * i], f[8 * g + 2 * i + 1], is_bf16) : 0u;
+                *reinterpret_cast<uint4*>(xp + g * 8) = y;
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                wp[i] = live ? pack2(act_apply(p.act, f[8 * g + 2 * i]), act_apply(p.act, f[8 * g + 2 * i + 1]), is_bf16) : 0u;
+            } else if (p.epilogue == HEXA_EPI_DACT) {
+              const uint4 y = *reinterpret_cast<const uint4*>(xp + g * 8);
+              const uint32_t* yp = reinterpret_cast<const uint32_t*>(&y);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                wp[i] = live ? pack2(f[8 * g + 2 * i] * act_grad(p.act, unpack_lo(yp[i], is_bf16)),
+                                     f[8 * g + 2 * i + 1] * act_grad(p.act, unpack_hi(yp[i], is_bf16)), is_bf16)
+                             : 0u;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) wp[i] = live ? pack2(f[8 * g + 2 * i], f[8 * g + 2 * i + 1], is_bf16) : 0u;
+            }
+            *reinterpret_cast<uint4*>(cp + g * 8) = w;
+          }
+        }
+      }
+      // accumulator drained: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {  // error path: give copies / MMAs in flight a bounded moment to land
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &ptr, 12000, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }
+  return fn;
+}
+
+// rank-2 or rank-3 map over 16-bit elements, 128-byte swizzle, zero fill out of bounds
+int make_map(CUtensorMap* tm, const void* base, int is_bf16, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+             const uint32_t* box) {
+  auto fn = encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return HEXA_ERR_CUDA; }
+  cuuint64_t d[3]; cuuint64_t s[2]; cuuint32_t b[3]; cuuint32_t es[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) s[i] = strides_bytes[i];
+  CUresult r = fn(tm, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank,
+                  const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (rank %d dims %llu,%llu box %u,%u)", (int)r, rank,
+              (unsigned long long)dims[0], (unsigned long long)dims[1], box[0], box[1]);
+    return HEXA_ERR_CUDA;
+  }
+  return HEXA_OK;
+}
+
+template <int BN, int MODE>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, int64_t max_tiles, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  HEXA_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    HEXA_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  int64_t grid = max_tiles < sm_count() ? max_tiles : sm_count();
+  if (grid <= 0) return HEXA_OK;
+  gemm_tc_kernel<BN, MODE><<<(unsigned)grid, kThreads, C::kSmemBytes, stream>>>(tmA, tmB, p);
+  HEXA_LAUNCH_CHECK("gemm_tc_kernel");
+  return HEXA_OK;
+}
+
+int mn_swap_flag() {
+  static int v = -1;
+  if (v < 0) { const char* s = getenv("HEXA_DEBUG_MN_SWAP"); v = (s && s[0] == '1') ? 1 : 0; }
+  return v;
+}
+
+}  // namespace
+
+bool esmm_tc_supported(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t b_estride, const void* aux,
+                       int64_t ldaux, const void* c, int64_t ldc, const float* bias, int64_t ldbias, int64_t n_out,
+                       int dtype) {
+  if (dtype != HEXA_F16 && dtype != HEXA_BF16) return false;
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c) || (aux && !aligned16(aux)) || (bias && !aligned16(bias))) return false;
+  if (lda % 8 || ldb % 8 || b_estride % 8 || ldc % 8 || (aux && ldaux % 8) || (bias && ldbias % 4) || n_out % 8) return false;
+  return true;
+}
+
+int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
+                   const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
+                   const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token, int E,
+                   int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue, int act, cudaStream_t stream) {
+  if (row_cap == 0) return HEXA_OK;
+  const int is_bf16 = dtype == HEXA_BF16;
+  const int BN = n_out > 128 ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[2] = {(uint64_t)k, (uint64_t)row_cap};
+    uint64_t str[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {BLOCK_K, BLOCK_M};
+    int rc = make_map(&tmA, a, is_bf16, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  if (b_layout == HEXA_B_NK) {
+    uint64_t dims[3] = {(uint64_t)k, (uint64_t)n_out, (uint64_t)E};
+    uint64_t str[2] = {(uint64_t)ldb * 2, (uint64_t)b_estride * 2};
+    uint32_t box[3] = {BLOCK_K, (uint32_t)BN, 1};
+    int rc = make_map(&tmB, b, is_bf16, 3, dims, str, box);
+    if (rc) return rc;
+  } else {
+    uint64_t dims[3] = {(uint64_t)n_out, (uint64_t)k, (uint64_t)E};
+    uint64_t str[2] = {(uint64_t)ldb * 2, (uint64_t)b_estride * 2};
+    uint32_t box[3] = {64, BLOCK_K, 1};
+    int rc = make_map(&tmB, b, is_bf16, 3, dims, str, box);
+    if (rc) return rc;
+  }
+  Params p{};
+  p.tile_expert = tile_expert; p.pad_offsets = pad_offsets; p.row_token = row_token;
+  p.bias = bias; p.ldbias = ldbias; p.aux = aux; p.ldaux = ldaux; p.c = c; p.ldc = ldc;
+  p.n = n_out; p.k = k; p.m = 0; p.E = E; p.epilogue = epilogue; p.act = act; p.is_bf16 = is_bf16;
+  p.mn_swap = mn_swap_flag(); p.status = status_word();
+  const int64_t max_tiles = (row_cap / BLOCK_M) * ceil_div(n_out, BN);
+  if (b_layout == HEXA_B_NK)
+    return BN == 256 ? launch<256, ESMM_NK>(tmA, tmB, p, max_tiles, stream) : launch<128, ESMM_NK>(tmA, tmB, p, max_tiles, stream);
+  return BN == 256 ? launch<256, ESMM_KN>(tmA, tmB, p, max_tiles, stream) : launch<128, ESMM_KN>(tmA, tmB, p, max_tiles, stream);
+}
+
+bool estmm_tc_supported(const void* p, int64_t ldp, const void* q, int64_t ldq, const void* out, int64_t ldo,
+                        int64_t o_estride, int64_t n, int dtype, int out_dtype) {
+  if (dtype != HEXA_F16 && dtype != HEXA_BF16) return false;
+  if (out_dtype != HEXA_F32 && out_dtype != dtype) return false;
+  if (!aligned16(p) || !aligned16(q) || !aligned16(out)) return false;
+  const int ov = out_dtype == HEXA_F32 ? 4 : 8;
+  if (ldp % 8 || ldq % 8 || ldo % ov || o_estride % ov || n % 8) return false;
+  return true;
+}
+
+int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets, int E,
+                    int64_t row_cap, int64_t m, int64_t n, void* out, int64_t ldo, int64_t o_estride, int dtype,
+                    int out_dtype, int beta, cudaStream_t stream) {
+  const int is_bf16 = dtype == HEXA_BF16;
+  const int BN = n > 128 ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  // the maps need at least one row even when no token was routed
+  const uint64_t rows = row_cap > 0 ? (uint64_t)row_cap : 1;
+  {
+    uint64_t dims[2] = {(uint64_t)m, rows};
+    uint64_t str[1] = {(uint64_t)ldp * 2};
+    uint32_t box[2] = {64, BLOCK_K};
+    int rc = make_map(&tmA, pp, is_bf16, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)n, rows};
+    uint64_t str[1] = {(uint64_t)ldq * 2};
+    uint32_t box[2] = {64, BLOCK_K};
+    int rc = make_map(&tmB, q, is_bf16, 2, dims, str, box);
+    if (rc) return rc;
+  }
+  Params p{};
+  p.pad_offsets = pad_offsets; p.c = out; p.ldc = ldo; p.c_estride = o_estride; p.n = n; p.m = m; p.E = E;
+  p.is_bf16 = is_bf16; p.out_f32 = out_dtype == HEXA_F32; p.beta = beta; p.mn_swap = mn_swap_flag();
+  p.status = status_word();
+  const int64_t max_tiles = (int64_t)E * ceil_div(m, BLOCK_M) * ceil_div(n, BN);
+  return BN == 256 ? launch<256, ESTMM>(tmA, tmB, p, max_tiles, stream) : launch<128, ESTMM>(tmA, tmB, p, max_tiles, stream);
+}
+
+}  // namespace hexa

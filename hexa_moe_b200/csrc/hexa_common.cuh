@@ -1,0 +1,99 @@
+// Shared host/device helpers for the hexa_moe_b200 kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/hexa_moe_b200.h"
+
+namespace hexa {
+
+// ---- host-side error plumbing -----------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int32_t* status_word();  // per-thread device status word (may be null)
+
+#define HEXA_REQUIRE(cond, ...)          \
+  do {                                   \
+    if (!(cond)) {                       \
+      ::hexa::set_error(__VA_ARGS__);    \
+      return HEXA_ERR_INVALID;           \
+    }                                    \
+  } while (0)
+
+#define HEXA_CUDA(call)                                                              \
+  do {                                                                               \
+    cudaError_t e_ = (call);                                                         \
+    if (e_ != cudaSuccess) {                                                         \
+      ::hexa::set_error("%s failed: %s", #call, cudaGetErrorString(e_));             \
+      return HEXA_ERR_CUDA;                                                          \
+    }                                                                                \
+  } while (0)
+
+#define HEXA_LAUNCH_CHECK(name)                                                      \
+  do {                                                                               \
+    cudaError_t e_ = cudaGetLastError();                                             \
+    if (e_ != cudaSuccess) {                                                         \
+      ::hexa::set_error("launch of %s failed: %s", name, cudaGetErrorString(e_));    \
+      return HEXA_ERR_CUDA;                                                          \
+    }                                                                                \
+  } while (0)
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline size_t dtype_size(int dt) { return dt == HEXA_F32 ? 4 : 2; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+int sm_count();  // SMs of the current device (cached per device)
+
+constexpr int kRowTile = 128;  // rows per GEMM tile == required segment alignment of the GEMM operators
+
+// ---- device-side scalar conversion ------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---- activations (value and derivative), shared by every epilogue ------------------------------
+__device__ __forceinline__ float act_apply(int act, float x) {
+  switch (act) {
+    case HEXA_ACT_RELU: return x > 0.f ? x : 0.f;
+    case HEXA_ACT_GELU: return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+    case HEXA_ACT_GELU_TANH: {
+      float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.f + tanhf(u));
+    }
+    case HEXA_ACT_SILU: return x / (1.f + expf(-x));
+    default: return x;
+  }
+}
+
+__device__ __forceinline__ float act_grad(int act, float x) {
+  switch (act) {
+    case HEXA_ACT_RELU: return x > 0.f ? 1.f : 0.f;
+    case HEXA_ACT_GELU: {
+      float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
+      float pdf = 0.3989422804014327f * expf(-0.5f * x * x);
+      return cdf + x * pdf;
+    }
+    case HEXA_ACT_GELU_TANH: {
+      float x2 = x * x;
+      float u = 0.7978845608028654f * (x + 0.044715f * x * x2);
+      float t = tanhf(u);
+      float du = 0.7978845608028654f * (1.f + 3.f * 0.044715f * x2);
+      return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
+    }
+    case HEXA_ACT_SILU: {
+      float s = 1.f / (1.f + expf(-x));
+      return s * (1.f + x * (1.f - s));
+    }
+    default: return 1.f;
+  }
+}
+
+}  // namespace hexa

@@ -1,0 +1,71 @@
+// C-ABI entry points of the GEMM-shaped operators: argument checks and engine selection.
+#include "hexa_common.cuh"
+
+namespace hexa {
+int esmm_simt_launch(const void*, int64_t, const void*, int, int64_t, int64_t, const float*, int64_t, void*, int64_t, void*,
+                     int64_t, const int32_t*, const int32_t*, const int32_t*, int, int64_t, int64_t, int64_t, int, int, int,
+                     cudaStream_t);
+int estmm_simt_launch(const void*, int64_t, const void*, int64_t, const int32_t*, int, int64_t, int64_t, void*, int64_t,
+                      int64_t, int, int, int, cudaStream_t);
+bool esmm_tc_supported(const void*, int64_t, const void*, int64_t, int64_t, const void*, int64_t, const void*, int64_t,
+                       const float*, int64_t, int64_t, int);
+int esmm_tc_launch(const void*, int64_t, const void*, int, int64_t, int64_t, const float*, int64_t, void*, int64_t, void*,
+                   int64_t, const int32_t*, const int32_t*, const int32_t*, int, int64_t, int64_t, int64_t, int, int, int,
+                   cudaStream_t);
+bool estmm_tc_supported(const void*, int64_t, const void*, int64_t, const void*, int64_t, int64_t, int64_t, int, int);
+int estmm_tc_launch(const void*, int64_t, const void*, int64_t, const int32_t*, int, int64_t, int64_t, int64_t, void*, int64_t,
+                    int64_t, int, int, int, cudaStream_t);
+}  // namespace hexa
+
+using namespace hexa;
+
+extern "C" int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
+                         const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
+                         const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token, int E,
+                         int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue, int act, int engine,
+                         void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  HEXA_REQUIRE(a && b && c && tile_expert && pad_offsets, "hexa_esmm: null pointer");
+  HEXA_REQUIRE(E > 0 && row_cap >= 0 && row_cap % kRowTile == 0 && n_out > 0 && k > 0,
+               "hexa_esmm: bad sizes (row_capacity must be a multiple of %d)", kRowTile);
+  HEXA_REQUIRE(lda >= k && ldc >= n_out && (!aux || ldaux >= n_out) && (!bias || ldbias >= n_out), "hexa_esmm: leading dimension too small");
+  HEXA_REQUIRE(b_layout == HEXA_B_NK || b_layout == HEXA_B_KN, "hexa_esmm: bad b_layout %d", b_layout);
+  HEXA_REQUIRE(ldb >= (b_layout == HEXA_B_NK ? k : n_out), "hexa_esmm: ldb too small");
+  HEXA_REQUIRE(dtype == HEXA_F32 || dtype == HEXA_F16 || dtype == HEXA_BF16, "hexa_esmm: bad dtype %d", dtype);
+  HEXA_REQUIRE(epilogue >= HEXA_EPI_LINEAR && epilogue <= HEXA_EPI_DACT, "hexa_esmm: bad epilogue %d", epilogue);
+  HEXA_REQUIRE(act >= HEXA_ACT_NONE && act <= HEXA_ACT_SILU, "hexa_esmm: bad activation %d", act);
+  HEXA_REQUIRE(epilogue != HEXA_EPI_DACT || aux, "hexa_esmm: HEXA_EPI_DACT needs the saved pre-activation in aux");
+  HEXA_REQUIRE(engine >= HEXA_ENGINE_AUTO && engine <= HEXA_ENGINE_SIMT, "hexa_esmm: bad engine %d", engine);
+  const bool tc_ok = esmm_tc_supported(a, lda, b, ldb, b_estride, aux, ldaux, c, ldc, bias, ldbias, n_out, dtype);
+  if (engine == HEXA_ENGINE_TCGEN05 && !tc_ok) {
+    set_error("hexa_esmm: tcgen05 engine needs 16-bit data, 16-byte aligned pointers and leading dimensions / n_out that are multiples of 8");
+    return HEXA_ERR_UNSUPPORTED;
+  }
+  if (engine != HEXA_ENGINE_SIMT && tc_ok)
+    return esmm_tc_launch(a, lda, b, b_layout, ldb, b_estride, bias, ldbias, aux, ldaux, c, ldc, tile_expert, pad_offsets,
+                          row_token, E, row_cap, n_out, k, dtype, epilogue, act, stream);
+  return esmm_simt_launch(a, lda, b, b_layout, ldb, b_estride, bias, ldbias, aux, ldaux, c, ldc, tile_expert, pad_offsets,
+                          row_token, E, row_cap, n_out, k, dtype, epilogue, act, stream);
+}
+
+extern "C" int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets, int E,
+                          int64_t row_cap, int64_t m, int64_t n, void* out, int64_t ldo, int64_t o_estride, int dtype,
+                          int out_dtype, int beta, int engine, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  HEXA_REQUIRE(p && q && out && pad_offsets, "hexa_estmm: null pointer");
+  HEXA_REQUIRE(E > 0 && row_cap >= 0 && row_cap % kRowTile == 0 && m > 0 && n > 0,
+               "hexa_estmm: bad sizes (row_capacity must be a multiple of %d)", kRowTile);
+  HEXA_REQUIRE(ldp >= m && ldq >= n && ldo >= n && o_estride >= (m - 1) * ldo + n, "hexa_estmm: leading dimension too small");
+  HEXA_REQUIRE(dtype == HEXA_F32 || dtype == HEXA_F16 || dtype == HEXA_BF16, "hexa_estmm: bad dtype %d", dtype);
+  HEXA_REQUIRE(out_dtype == HEXA_F32 || out_dtype == dtype, "hexa_estmm: out_dtype must be fp32 or the input dtype");
+  HEXA_REQUIRE(beta == 0 || beta == 1, "hexa_estmm: beta must be 0 or 1");
+  HEXA_REQUIRE(engine >= HEXA_ENGINE_AUTO && engine <= HEXA_ENGINE_SIMT, "hexa_estmm: bad engine %d", engine);
+  const bool tc_ok = estmm_tc_supported(p, ldp, q, ldq, out, ldo, o_estride, n, dtype, out_dtype);
+  if (engine == HEXA_ENGINE_TCGEN05 && !tc_ok) {
+    set_error("hexa_estmm: tcgen05 engine needs 16-bit inputs, 16-byte aligned pointers and leading dimensions / n that are multiples of 8");
+    return HEXA_ERR_UNSUPPORTED;
+  }
+  if (engine != HEXA_ENGINE_SIMT && tc_ok)
+    return estmm_tc_launch(p, ldp, q, ldq, pad_offsets, E, row_cap, m, n, out, ldo, o_estride, dtype, out_dtype, beta, stream);
+  return estmm_simt_launch(p, ldp, q, ldq, pad_offsets, E, m, n, out, ldo, o_estride, dtype, out_dtype, beta, stream);
+}

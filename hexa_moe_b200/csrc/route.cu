@@ -1,0 +1,250 @@
+// Routing: segment the T*top_k routed rows into contiguous, padded per-expert segments.
+//
+// Three launches, no host synchronisation, deterministic (equal to a stable sort by expert):
+//   1. route_hist    each warp histograms one chunk of kRowsPerWarp routed rows
+//   2. route_scan    one block: per-expert exclusive scan over chunks, per-expert totals, padded
+//                    segment offsets, tile -> expert table, -1 in the pad slots
+//   3. route_scatter each warp re-reads its chunk and places every row at
+//                    pad_offsets[e] + (rows of e in earlier chunks) + (rows of e earlier in the chunk)
+// HBM traffic: ids are read twice (8 B per routed row), row_token and token_row written once.
+#include <stdarg.h>
+
+#include "hexa_common.cuh"
+
+namespace hexa {
+namespace {
+
+constexpr int kRowsPerWarp = 512;
+constexpr int kMaxExperts = 4096;  // keeps both shared-memory tables under 48 KB
+
+__device__ __forceinline__ int load_id(const int32_t* ids, int64_t f, int64_t T, int64_t stride_t, int64_t stride_k) {
+  int64_t j = f / T;
+  int64_t t = f - j * T;
+  return ids[t * stride_t + j * stride_k];
+}
+
+__global__ void route_hist(const int32_t* __restrict__ ids, int64_t T, int64_t n_rows, int64_t stride_t,
+                           int64_t stride_k, int E, int32_t* __restrict__ chunk_hist) {
+  extern __shared__ int32_t sm[];
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int32_t* h = sm + warp * E;
+  for (int e = lane; e < E; e += 32) h[e] = 0;
+  __syncwarp();
+  const int64_t chunk = (int64_t)blockIdx.x * warps + warp;
+  const int64_t begin = chunk * kRowsPerWarp;
+  if (begin < n_rows) {
+    const int64_t end = min(begin + (int64_t)kRowsPerWarp, n_rows);
+    for (int64_t f = begin + lane; f < end; f += 32) {
+      int e = load_id(ids, f, T, stride_t, stride_k);
+      if (e >= 0 && e < E) atomicAdd(&h[e], 1);
+    }
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) chunk_hist[chunk * E + e] = h[e];
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+route_scan(int32_t* __restrict__ chunk_hist, int64_t n_chunks, int E, int align, int64_t row_capacity,
+           int32_t* __restrict__ counts, int32_t* __restrict__ seg_offsets, int32_t* __restrict__ pad_offsets,
+           int32_t* __restrict__ row_token, int32_t* __restrict__ tile_expert) {
+  extern __shared__ int32_t sm[];
+  int32_t* s_cnt = sm;          // [E]
+  int32_t* s_pad = sm + E;      // [E + 1]
+  // per-expert exclusive scan over chunks (thread per expert: coalesced across experts)
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int32_t run = 0;
+    int64_t c = 0;
+    for (; c + 4 <= n_chunks; c += 4) {
+      int32_t v0 = chunk_hist[(c + 0) * E + e], v1 = chunk_hist[(c + 1) * E + e];
+      int32_t v2 = chunk_hist[(c + 2) * E + e], v3 = chunk_hist[(c + 3) * E + e];
+      chunk_hist[(c + 0) * E + e] = run; run += v0;
+      chunk_hist[(c + 1) * E + e] = run; run += v1;
+      chunk_hist[(c + 2) * E + e] = run; run += v2;
+      chunk_hist[(c + 3) * E + e] = run; run += v3;
+    }
+    for (; c < n_chunks; ++c) {
+      int32_t v = chunk_hist[c * E + e];
+      chunk_hist[c * E + e] = run; run += v;
+    }
+    s_cnt[e] = run;
+    counts[e] = run;
+  }
+  __syncthreads();
+  // exclusive scans over experts (unpadded and padded) by warp 0, 32 experts per step
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int32_t carry_seg = 0, carry_pad = 0;
+    for (int base = 0; base < E; base += 32) {
+      int e = base + lane;
+      int32_t c = e < E ? s_cnt[e] : 0;
+      int32_t p = (c + align - 1) / align * align;
+      int32_t ic = c, ip = p;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int32_t tc = __shfl_up_sync(0xffffffffu, ic, o), tp = __shfl_up_sync(0xffffffffu, ip, o);
+        if (lane >= o) { ic += tc; ip += tp; }
+      }
+      if (e < E) {
+        seg_offsets[e] = carry_seg + ic - c;
+        int32_t po = carry_pad + ip - p;
+        pad_offsets[e] = po;
+        s_pad[e] = po;
+      }
+      carry_seg += __shfl_sync(0xffffffffu, ic, 31);
+      carry_pad += __shfl_sync(0xffffffffu, ip, 31);
+    }
+    if (lane == 0) {
+      seg_offsets[E] = carry_seg;
+      pad_offsets[E] = carry_pad;
+      s_pad[E] = carry_pad;
+    }
+  }
+  __syncthreads();
+  // tile -> expert: binary search for the segment that holds the tile's first row
+  const int64_t n_tiles = row_capacity / align;
+  const int32_t n_pad = s_pad[E];
+  for (int64_t i = threadIdx.x; i < n_tiles; i += blockDim.x) {
+    int32_t row = (int32_t)(i * align);
+    int32_t val = -1;
+    if (row < n_pad) {
+      int lo = 0, hi = E;  // largest e with s_pad[e] <= row (empty experts share an offset: take the last)
+      while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (s_pad[mid] <= row) lo = mid; else hi = mid;
+      }
+      val = lo;
+    }
+    tile_expert[i] = val;
+  }
+  // pad slots of every segment
+  for (int64_t i = threadIdx.x; i < (int64_t)E * align; i += blockDim.x) {
+    int e = (int)(i / align), o = (int)(i % align);
+    int32_t slot = s_pad[e] + s_cnt[e] + o;
+    if (slot < s_pad[e + 1]) row_token[slot] = -1;
+  }
+}
+
+__global__ void route_scatter(const int32_t* __restrict__ ids, int64_t T, int top_k, int64_t n_rows, int64_t stride_t,
+                              int64_t stride_k, int E, const int32_t* __restrict__ chunk_base,
+                              const int32_t* __restrict__ pad_offsets, int32_t* __restrict__ row_token,
+                              int32_t* __restrict__ token_row) {
+  extern __shared__ int32_t sm[];
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int32_t* cur = sm + warp * E;
+  const int64_t chunk = (int64_t)blockIdx.x * warps + warp;
+  const int64_t begin = chunk * kRowsPerWarp;
+  if (begin >= n_rows) return;  // whole warp leaves together
+  for (int e = lane; e < E; e += 32) cur[e] = pad_offsets[e] + chunk_base[chunk * E + e];
+  __syncwarp();
+  const int64_t end = min(begin + (int64_t)kRowsPerWarp, n_rows);
+  for (int64_t f0 = begin; f0 < end; f0 += 32) {
+    const int64_t f = f0 + lane;
+    int e = -1;
+    int64_t j = 0, t = 0;
+    if (f < end) {
+      j = f / T; t = f - j * T;
+      e = ids[t * stride_t + j * stride_k];
+      if (e < 0 || e >= E) e = -1;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    int32_t pos = -1;
+    if (e >= 0) pos = cur[e] + rank;
+    __syncwarp();
+    if (e >= 0 && rank == 0) cur[e] += __popc(peers);
+    __syncwarp();
+    if (f < end) {
+      token_row[t * top_k + j] = pos;
+      if (pos >= 0) row_token[pos] = (int32_t)t;
+    }
+  }
+}
+
+}  // namespace
+
+// ---- error plumbing shared by every translation unit ------------------------------------------
+static thread_local char g_err[512] = "no error";
+static thread_local int32_t* g_status = nullptr;
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+int32_t* status_word() { return g_status; }
+
+int sm_count() {
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace hexa
+
+using namespace hexa;
+
+extern "C" int hexa_version(void) { return 100; }
+extern "C" const char* hexa_last_error_string(void) { return hexa::g_err; }
+extern "C" int hexa_set_status_word(int32_t* status) {
+  hexa::g_status = status;
+  return HEXA_OK;
+}
+
+extern "C" int64_t hexa_route_row_capacity(int64_t T, int top_k, int E, int align) {
+  if (T < 0 || top_k <= 0 || E <= 0 || align <= 0) return -1;
+  int64_t cap = T * top_k + (int64_t)E * (align - 1);
+  return ceil_div(cap, align) * align;
+}
+
+extern "C" size_t hexa_route_workspace_bytes(int64_t T, int top_k, int E) {
+  if (T < 0 || top_k <= 0 || E <= 0) return 0;
+  int64_t chunks = ceil_div(T * top_k, kRowsPerWarp);
+  if (chunks < 1) chunks = 1;
+  return (size_t)chunks * (size_t)E * sizeof(int32_t);
+}
+
+extern "C" int hexa_route(const int32_t* ids, int64_t T, int top_k, int64_t stride_t, int64_t stride_k, int E,
+                          int align, int32_t* counts, int32_t* seg_offsets, int32_t* pad_offsets,
+                          int32_t* row_token, int32_t* token_row, int32_t* tile_expert, void* workspace,
+                          size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  HEXA_REQUIRE(T >= 0 && top_k > 0 && E > 0 && E <= kMaxExperts && align > 0, "hexa_route: bad sizes T=%lld k=%d E=%d align=%d",
+               (long long)T, top_k, E, align);
+  HEXA_REQUIRE(T * top_k + (int64_t)E * align < (int64_t)INT32_MAX, "hexa_route: too many rows for int32 indices");
+  HEXA_REQUIRE(counts && seg_offsets && pad_offsets && row_token && token_row && tile_expert && workspace,
+               "hexa_route: null output or workspace pointer");
+  HEXA_REQUIRE(T == 0 || ids, "hexa_route: null ids");
+  const size_t need = hexa_route_workspace_bytes(T, top_k, E);
+  if (workspace_bytes < need) {
+    set_error("hexa_route: workspace %zu bytes < required %zu", workspace_bytes, need);
+    return HEXA_ERR_WORKSPACE;
+  }
+  const int64_t n_rows = T * top_k;
+  const int64_t n_chunks = ceil_div(n_rows, kRowsPerWarp);
+  const int64_t row_cap = hexa_route_row_capacity(T, top_k, E, align);
+  int32_t* chunk_hist = (int32_t*)workspace;
+  int warps = (int)(48 * 1024 / (4 * (int64_t)E));
+  warps = warps < 1 ? 1 : (warps > 8 ? 8 : warps);
+  const size_t smem = (size_t)warps * E * sizeof(int32_t);
+  if (n_chunks > 0) {
+    route_hist<<<(unsigned)ceil_div(n_chunks, warps), warps * 32, smem, stream>>>(ids, T, n_rows, stride_t, stride_k, E,
+                                                                                chunk_hist);
+    HEXA_LAUNCH_CHECK("route_hist");
+  }
+  route_scan<<<1, 1024, (2 * (size_t)E + 1) * sizeof(int32_t), stream>>>(chunk_hist, n_chunks, E, align, row_cap, counts,
+                                                                         seg_offsets, pad_offsets, row_token, tile_expert);
+  HEXA_LAUNCH_CHECK("route_scan");
+  if (n_chunks > 0) {
+    route_scatter<<<(unsigned)ceil_div(n_chunks, warps), warps * 32, smem, stream>>>(
+        ids, T, top_k, n_rows, stride_t, stride_k, E, chunk_hist, pad_offsets, row_token, token_row);
+    HEXA_LAUNCH_CHECK("route_scatter");
+  }
+  return HEXA_OK;
+}

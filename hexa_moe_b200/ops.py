@@ -1,0 +1,224 @@
+"""Tensor-level wrappers over the C ABI: routing, row movement, ESMM, ESTMM, ESS and the
+single-device MoE layer forward/backward assembled from them.
+
+Everything here runs CUDA kernels from libhexa_moe_b200.so on the current stream of the input's
+device; no function has a CPU or PyTorch fallback.  Buffers in "sorted-row" layout have
+`row_capacity` rows of which the first pad_offsets[E] are meaningful (pad rows hold zeros).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+from ._lib import check, dt, lib, ptr, stream_of
+
+
+@dataclass
+class Routing:
+    """Device-side result of `route` (all int32 tensors) plus the static sizes."""
+    counts: torch.Tensor        # [E]
+    seg_offsets: torch.Tensor   # [E+1] exclusive scan of counts
+    pad_offsets: torch.Tensor   # [E+1] segment starts, multiples of `align`
+    row_token: torch.Tensor     # [row_capacity] token of each sorted row, -1 for pad rows
+    token_row: torch.Tensor     # [T*k] sorted row of routed row (t, j) at t*k + j
+    tile_expert: torch.Tensor   # [row_capacity/align]
+    num_tokens: int
+    top_k: int
+    num_experts: int
+    align: int
+    row_capacity: int
+
+
+def route(ids: torch.Tensor, num_experts: int, align: int = L.ROW_TILE, route_major: bool = False) -> Routing:
+    """Segment routed rows by expert.  ids: int32 [T, k] (or [k, T] when route_major)."""
+    if ids.dtype != torch.int32:
+        raise L.HexaError("route: ids must be int32")
+    if ids.dim() != 2:
+        raise L.HexaError("route: ids must be 2-D")
+    if route_major:
+        k, T = ids.shape
+        st, sk = ids.stride(1), ids.stride(0)
+    else:
+        T, k = ids.shape
+        st, sk = ids.stride(0), ids.stride(1)
+    s = stream_of(ids)
+    dev = ids.device
+    cap = lib().hexa_route_row_capacity(T, k, num_experts, align)
+    if cap < 0:
+        raise L.HexaError("route: bad sizes")
+    i32 = dict(dtype=torch.int32, device=dev)
+    r = Routing(torch.empty(num_experts, **i32), torch.empty(num_experts + 1, **i32), torch.empty(num_experts + 1, **i32),
+                torch.empty(max(cap, 1), **i32), torch.empty(max(T * k, 1), **i32), torch.empty(max(cap // align, 1), **i32),
+                T, k, num_experts, align, cap)
+    ws_bytes = lib().hexa_route_workspace_bytes(T, k, num_experts)
+    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
+    check(lib().hexa_route(ptr(ids), T, k, st, sk, num_experts, align, ptr(r.counts), ptr(r.seg_offsets), ptr(r.pad_offsets),
+                           ptr(r.row_token), ptr(r.token_row), ptr(r.tile_expert), ptr(ws), ws.numel(), s), "hexa_route")
+    return r
+
+
+def _ld(t: torch.Tensor) -> int:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise L.HexaError("expected a 2-D tensor with unit inner stride")
+    return t.stride(0)
+
+
+def gather_rows(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Token order -> sorted rows: out[row] = src[row_token[row]] (zeros for pad rows)."""
+    cols = src.shape[1]
+    if out is None:
+        out = torch.empty(r.row_capacity, cols, dtype=src.dtype, device=src.device)
+    check(lib().hexa_gather_rows(ptr(src), _ld(src), ptr(r.row_token), ptr(r.pad_offsets), r.num_experts, r.row_capacity,
+                                 cols, ptr(out), _ld(out), dt(src), stream_of(src)), "hexa_gather_rows")
+    return out
+
+
+def combine_rows(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Sorted rows -> token order with the unweighted sum over the k routes."""
+    cols = src.shape[1]
+    if out is None:
+        out = torch.empty(r.num_tokens, cols, dtype=src.dtype, device=src.device)
+    check(lib().hexa_combine_rows(ptr(src), _ld(src), ptr(r.token_row), r.num_tokens, r.top_k, cols, ptr(out), _ld(out),
+                                  dt(src), stream_of(src)), "hexa_combine_rows")
+    return out
+
+
+def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Optional[torch.Tensor] = None,
+         epilogue: int = L.EPI_LINEAR, act: int = L.ACT_NONE, aux: Optional[torch.Tensor] = None,
+         out: Optional[torch.Tensor] = None, engine: int = L.ENGINE_AUTO, n_out: Optional[int] = None,
+         k: Optional[int] = None) -> torch.Tensor:
+    """c[row] = a[row] x b[expert(row)] with the fused epilogue.  b: [E, n_out, k] (B_NK) or [E, k, n_out] (B_KN);
+    b may be a view with arbitrary expert / row strides (unit inner stride)."""
+    if r.align % L.ROW_TILE:
+        raise L.HexaError("esmm: routing must be aligned to 128 rows")
+    if b.dim() != 3 or b.stride(2) != 1:
+        raise L.HexaError("esmm: b must be 3-D with unit inner stride")
+    if b_layout == L.B_NK:
+        nn, kk = b.shape[1], b.shape[2]
+    else:
+        kk, nn = b.shape[1], b.shape[2]
+    n_out = nn if n_out is None else n_out
+    k = kk if k is None else k
+    if a.dtype != b.dtype:
+        raise L.HexaError(f"esmm: a is {a.dtype} but b is {b.dtype}")
+    if bias is not None and bias.dtype != torch.float32:
+        raise L.HexaError("esmm: bias must be float32")
+    if out is None:
+        out = torch.empty(r.row_capacity, n_out, dtype=a.dtype, device=a.device)
+    check(lib().hexa_esmm(ptr(a), _ld(a), ptr(b), b_layout, b.stride(1), b.stride(0), ptr(bias),
+                          0 if bias is None else _ld(bias), ptr(aux), 0 if aux is None else _ld(aux), ptr(out), _ld(out),
+                          ptr(r.tile_expert), ptr(r.pad_offsets), ptr(r.row_token), r.num_experts, r.row_capacity, n_out, k,
+                          dt(a), epilogue, act, engine, stream_of(a)), "hexa_esmm")
+    return out
+
+
+def estmm(p: torch.Tensor, q: torch.Tensor, r: Routing, out_dtype: Optional[torch.dtype] = None,
+          out: Optional[torch.Tensor] = None, beta: int = 0, engine: int = L.ENGINE_AUTO) -> torch.Tensor:
+    """out[e] = p_e^T q_e over expert e's rows: [E, p.cols, q.cols]."""
+    if r.align % L.ROW_TILE:
+        raise L.HexaError("estmm: routing must be aligned to 128 rows")
+    m, n = p.shape[1], q.shape[1]
+    if p.dtype != q.dtype:
+        raise L.HexaError("estmm: p and q dtypes differ")
+    if out is None:
+        out_dtype = out_dtype or p.dtype
+        out = torch.empty(r.num_experts, m, n, dtype=out_dtype, device=p.device)
+        if beta:
+            raise L.HexaError("estmm: beta=1 needs an existing out")
+    if out.stride(2) != 1:
+        raise L.HexaError("estmm: out must have unit inner stride")
+    check(lib().hexa_estmm(ptr(p), _ld(p), ptr(q), _ld(q), ptr(r.pad_offsets), r.num_experts, r.row_capacity, m, n, ptr(out),
+                           out.stride(1), out.stride(0), dt(p), dt(out), beta, engine, stream_of(p)), "hexa_estmm")
+    return out
+
+
+def ess(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[e] = sum of expert e's rows of src, float32 [E, cols]."""
+    if r.align % L.ROW_TILE:
+        raise L.HexaError("ess: routing must be aligned to 128 rows")
+    cols = src.shape[1]
+    if out is None:
+        out = torch.empty(r.num_experts, cols, dtype=torch.float32, device=src.device)
+    nbytes = lib().hexa_ess_workspace_bytes(r.row_capacity, cols)
+    ws = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=src.device)
+    check(lib().hexa_ess(ptr(src), _ld(src), ptr(r.pad_offsets), r.num_experts, r.row_capacity, cols, ptr(out), _ld(out),
+                         dt(src), ptr(ws), ws.numel(), stream_of(src)), "hexa_ess")
+    return out
+
+
+def mask_pad_rows(buf: torch.Tensor, r: Routing) -> torch.Tensor:
+    check(lib().hexa_mask_pad_rows(ptr(buf), _ld(buf), ptr(r.row_token), ptr(r.pad_offsets), r.num_experts, r.row_capacity,
+                                   buf.shape[1], dt(buf), stream_of(buf)), "hexa_mask_pad_rows")
+    return buf
+
+
+# -------------------------------------------------------------------------------------------------
+# one MoE layer on one device
+# -------------------------------------------------------------------------------------------------
+@dataclass
+class LayerState:
+    """What the backward of a layer needs (all in sorted-row layout)."""
+    routing: Routing
+    xs: torch.Tensor      # gathered input rows  [cap, d]
+    y1: torch.Tensor      # fc1 pre-activation   [cap, H]
+    h: torch.Tensor       # act(y1)              [cap, H]
+    act_grad: Optional[torch.Tensor] = None   # act'(y1) when the activation is not a fused one
+
+
+def _f32(t):
+    return None if t is None else t.detach().to(torch.float32).contiguous()
+
+
+def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=False, engine=L.ENGINE_AUTO,
+                need_state=True):
+    """y[t] = sum_j fc2(act(fc1(x[t]; e_j)); e_j).  x [T,d]; ids int32 [T,k] ([k,T] if route_major);
+    w1 [E,H,d]; w2 [E,H,d_out]; b1 [E,H] / b2 [E,d_out] or None.
+    act_id: an _lib.ACT_* id fused into the fc1 epilogue, or -1 to call `act_fn` (any elementwise
+    callable) between the two ESMMs.  Returns (y [T,d_out], LayerState)."""
+    E = w1.shape[0]
+    r = route(ids, E, L.ROW_TILE, route_major=route_major)
+    xs = gather_rows(x, r)
+    b1f, b2f = _f32(b1), _f32(b2)
+    H = w1.shape[1]
+    y1 = torch.empty(r.row_capacity, H, dtype=x.dtype, device=x.device)
+    g = None
+    if act_id >= 0:
+        h = esmm(xs, w1, L.B_NK, r, b1f, L.EPI_ACT, act_id, aux=y1, engine=engine)
+    else:
+        esmm(xs, w1, L.B_NK, r, b1f, L.EPI_LINEAR, out=y1, engine=engine)
+        if need_state:
+            with torch.enable_grad():
+                yy = y1.detach().requires_grad_(True)
+                hh = act_fn(yy)
+                (g,) = torch.autograd.grad(hh.sum(), yy)
+            h = hh.detach().contiguous()
+        else:
+            h = act_fn(y1).contiguous()
+        mask_pad_rows(h, r)
+    ys = esmm(h, w2, L.B_KN, r, b2f, L.EPI_LINEAR, engine=engine)
+    y = combine_rows(ys, r)
+    return y, (LayerState(r, xs, y1, h, g) if need_state else None)
+
+
+def moe_backward(st: LayerState, dy, w1, w2, act_id: int, has_b1=True, has_b2=True, grad_dtype=None,
+                 engine=L.ENGINE_AUTO):
+    """Gradients of moe_forward.  Returns (dx [T,d], dw1 [E,H,d], dw2 [E,H,d_out], db1 [E,H] | None,
+    db2 [E,d_out] | None); bias gradients are float32, weight gradients `grad_dtype` (default: dtype of dy)."""
+    r = st.routing
+    dys = gather_rows(dy.contiguous(), r)
+    db2 = ess(dys, r) if has_b2 else None
+    dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine)
+    if act_id >= 0:
+        dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_DACT, act_id, aux=st.y1, engine=engine)
+    else:
+        dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_LINEAR, engine=engine)
+        dh.mul_(st.act_grad)
+        mask_pad_rows(dh, r)
+    db1 = ess(dh, r) if has_b1 else None
+    dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine)
+    dxs = esmm(dh, w1, L.B_KN, r, None, L.EPI_LINEAR, engine=engine)
+    dx = combine_rows(dxs, r)
+    return dx, dw1, dw2, db1, db2

@@ -1,0 +1,155 @@
+/*
+ * hexa_moe_b200 - C ABI of the B200 (sm_100a) expert-specific MoE operators.
+ *
+ * Every entry point takes plain device pointers, sizes, leading dimensions and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t).  Unless a comment says otherwise an entry point
+ * allocates nothing, never synchronises with the host and never exits the process: scratch memory
+ * is supplied by the caller (query the size with the matching *_workspace_bytes function).
+ * Return value: HEXA_OK or a negative hexa_status; hexa_last_error_string() describes the
+ * last failure on the calling thread.
+ *
+ * Layout shared by all operators ("sorted rows"): the N = T*top_k routed rows of a layer are
+ * numbered f = j*T + t (route-major) and stably sorted by expert; expert e owns rows
+ * [pad_offsets[e], pad_offsets[e] + counts[e]) and its segment is padded with empty rows up to
+ * pad_offsets[e+1], a multiple of `align`.  row_token[r] is the token of row r or -1 for a pad
+ * row; token_row[t*top_k + j] is the row of routed row (t,j); tile_expert[r/align] is the expert
+ * that owns the `align`-row tile.  Pad rows of every activation buffer hold zeros.
+ *
+ * Replaces, in the reference (paths inside the UNITES-Lab/HEXA-MoE repository):
+ *   hexa_moe_cuda/hexa_moe/include/hexa_moe.h:3-181      (13 raw-pointer launchers)
+ *   hexa_moe_cuda/hexa_moe/torch/hexa_moe_ops.cpp:9-301  (pybind11 module hexa_moe_cuda)
+ *   hexa_moe_triton/hexa_moe/kernels/{basics,esmm,fused}.py (counter / ESMM / es_fused)
+ */
+#ifndef HEXA_MOE_B200_H
+#define HEXA_MOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  HEXA_OK = 0,
+  HEXA_ERR_INVALID = -1,      /* bad argument (null pointer, size, alignment, enum) */
+  HEXA_ERR_CUDA = -2,         /* a CUDA runtime / driver call failed */
+  HEXA_ERR_UNSUPPORTED = -3,  /* valid request that this build has no kernel for */
+  HEXA_ERR_WORKSPACE = -4,    /* caller-supplied workspace too small */
+  HEXA_ERR_DEVICE = -5        /* a kernel reported a failure through its status word */
+} hexa_status;
+
+typedef enum { HEXA_F32 = 0, HEXA_F16 = 1, HEXA_BF16 = 2 } hexa_dtype;
+
+/* Activation fused into the ESMM epilogue (HEXA_ACT_NONE: plain linear). */
+typedef enum {
+  HEXA_ACT_NONE = 0,
+  HEXA_ACT_RELU = 1,
+  HEXA_ACT_GELU = 2,       /* exact, erf based (torch.nn.functional.gelu default) */
+  HEXA_ACT_GELU_TANH = 3,
+  HEXA_ACT_SILU = 4
+} hexa_act;
+
+/* Layout of the per-expert B operand of hexa_esmm. */
+typedef enum {
+  HEXA_B_NK = 0, /* b[e] is [n_out, k], k contiguous: c = a * b[e]^T (fc1 forward, fc2 dgrad)   */
+  HEXA_B_KN = 1  /* b[e] is [k, n_out], n_out contiguous: c = a * b[e] (fc2 forward, fc1 dgrad) */
+} hexa_b_layout;
+
+/* Epilogue of hexa_esmm. */
+typedef enum {
+  HEXA_EPI_LINEAR = 0, /* c = acc + bias                                                          */
+  HEXA_EPI_ACT = 1,    /* aux (if non-null) = acc + bias ; c = act(acc + bias)                    */
+  HEXA_EPI_DACT = 2    /* c = acc * act'(aux)   (aux holds the saved pre-activation)              */
+} hexa_epilogue;
+
+/* Which kernel family executes a GEMM-shaped operator. */
+typedef enum {
+  HEXA_ENGINE_AUTO = 0, /* tcgen05 when dtype/alignment allow it, otherwise the CUDA-core kernel  */
+  HEXA_ENGINE_TCGEN05 = 1,
+  HEXA_ENGINE_SIMT = 2  /* fp32-accumulating CUDA-core kernel (the only one for HEXA_F32)         */
+} hexa_engine;
+
+/* Library / error reporting.  Replaces HandleError's printf+exit(1)
+ * (hexa_moe_cuda/hexa_moe/kernels/esmm_half.cu:27-36). */
+int hexa_version(void);
+const char* hexa_last_error_string(void);
+
+/* Device status word for kernels with bounded waits (mbarrier spins in the tcgen05 kernels).
+ * `status` points to one int32 in device memory that the caller zeroes once; a kernel that gives
+ * up a wait stores a non-zero code there and returns.  Pass it with hexa_set_status_word (per
+ * host thread); NULL disables reporting (waits stay bounded). */
+int hexa_set_status_word(int32_t* status);
+
+/* ---- routing: replaces launch_count + launch_assign (include/hexa_moe.h:3-22,
+ *      kernels/shared_cuda_core.cu:128-182, 285-333) and kernels/basics.py:counter (89-118) ---- */
+
+/* Upper bound on padded rows: T*top_k + E*(align-1), rounded up to a multiple of align. */
+int64_t hexa_route_row_capacity(int64_t num_tokens, int top_k, int num_experts, int align);
+size_t hexa_route_workspace_bytes(int64_t num_tokens, int top_k, int num_experts);
+
+/* ids: expert id of routed row (t,j) at ids[t*stride_t + j*stride_k]; ids outside [0,E) are
+ * skipped (their token_row entry is -1).
+ * Outputs (device, int32): counts[E], seg_offsets[E+1] (exclusive scan of counts),
+ * pad_offsets[E+1], row_token[row_capacity], token_row[T*top_k], tile_expert[row_capacity/align]
+ * (-1 beyond pad_offsets[E]).  Results are deterministic: identical to a stable sort. */
+int hexa_route(const int32_t* ids, int64_t num_tokens, int top_k, int64_t stride_t, int64_t stride_k,
+               int num_experts, int align, int32_t* counts, int32_t* seg_offsets, int32_t* pad_offsets,
+               int32_t* row_token, int32_t* token_row, int32_t* tile_expert, void* workspace,
+               size_t workspace_bytes, void* stream);
+
+/* ---- row movement between token order and sorted-row order (the reference gathers rows by
+ *      tok_ids inside its kernels, kernels/esmm.py:95-101, and sums the k routes in Python,
+ *      impls/layers.py:254-258) ---- */
+
+/* dst[r,:] = row_token[r] >= 0 ? src[row_token[r],:] : 0   for r < pad_offsets[E]. */
+int hexa_gather_rows(const void* src, int64_t src_ld, const int32_t* row_token, const int32_t* pad_offsets,
+                     int num_experts, int64_t row_capacity, int64_t cols, void* dst, int64_t dst_ld,
+                     int dtype, void* stream);
+
+/* dst[t,:] = sum_j src[token_row[t*top_k + j],:] (fp32 accumulation, fixed order j = 0..k-1). */
+int hexa_combine_rows(const void* src, int64_t src_ld, const int32_t* token_row, int64_t num_tokens,
+                      int top_k, int64_t cols, void* dst, int64_t dst_ld, int dtype, void* stream);
+
+/* ---- ESMM: replaces launch_esmm_accum_shared_tensor_{full,mix,half} (include/hexa_moe.h:24-72)
+ *      and the ESMM part of launch_fused_grad_* ; kernels/esmm.py:ESMM (249-295),
+ *      kernels/fused.py:142-182 ----
+ * For every sorted row r < pad_offsets[E] with e = tile_expert[r/128]:
+ *   acc[r,:] = a[r,:] (1 x k) times b[e] (layout per b_layout), fp32 accumulation, then `epilogue`.
+ * a [row_capacity, k] (lda), c [row_capacity, n_out] (ldc), aux like c (ldaux) or NULL,
+ * bias fp32 [E, n_out] (ldbias) or NULL, b expert stride b_estride and row stride ldb in elements.
+ * Rows with row_token[r] < 0 are written as zeros.  Segments must be aligned to 128 rows. */
+int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
+              const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
+              const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
+              int num_experts, int64_t row_capacity, int64_t n_out, int64_t k, int dtype, int epilogue,
+              int act, int engine, void* stream);
+
+/* ---- ESTMM: replaces task 1 of launch_fused_grad_* (include/hexa_moe.h:74-181),
+ *      kernels/fused.py:183-235 (operator definition; the reference kernels mis-handle segments
+ *      longer than 16 rows) ----
+ * out[e] (m x n, ld ldo, expert stride o_estride) = beta*out[e] + sum over rows r of expert e of
+ * p[r,:m]^T (outer) q[r,:n].  Experts without rows get beta*out[e] (zeros for beta = 0).
+ * p [row_capacity, m] (ldp), q [row_capacity, n] (ldq) in `dtype`; out in `out_dtype`
+ * (HEXA_F32 or `dtype`); beta is 0 or 1. */
+int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets,
+               int num_experts, int64_t row_capacity, int64_t m, int64_t n, void* out, int64_t ldo,
+               int64_t o_estride, int dtype, int out_dtype, int beta, int engine, void* stream);
+
+/* ---- ESS: replaces task 2 of launch_fused_grad_bias_*, kernels/fused.py:111-141 ----
+ * out[e,:] = sum of src rows of expert e, fp32 [E, cols] (ldo).  Deterministic two-pass
+ * reduction; workspace holds one fp32 partial row per 128 sorted rows. */
+size_t hexa_ess_workspace_bytes(int64_t row_capacity, int64_t cols);
+int hexa_ess(const void* src, int64_t src_ld, const int32_t* pad_offsets, int num_experts,
+             int64_t row_capacity, int64_t cols, float* out, int64_t ldo, int dtype, void* workspace,
+             size_t workspace_bytes, void* stream);
+
+/* Elementwise helper on sorted rows for activations the epilogue does not know:
+ * dst[r,:] = row_token[r] >= 0 ? src[r,:] : 0 (restores the zero-pad-row invariant). */
+int hexa_mask_pad_rows(void* buf, int64_t ld, const int32_t* row_token, const int32_t* pad_offsets,
+                       int num_experts, int64_t row_capacity, int64_t cols, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HEXA_MOE_B200_H */
