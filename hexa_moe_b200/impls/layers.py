@@ -1,0 +1,291 @@
+"""Autograd functions of the FFN / MoE layers and the collectives around them.
+
+Function-level contract of the reference (hexa_moe/impls/layers.py:18-478), kept:
+
+    FusedMoE_Shared_CudaCore.apply(config, x[T,d], fc1_w[E,loc,d], fc2_w[E,loc,d_out],
+                                   fc1_b[E,loc] | None, fc2_b[E,d_out] | None) -> y[T,d_out]
+    MLP_Implement.apply(config, x[T,d], fc1_w[H,d], fc2_w[H,d_out], fc1_b[H] | None, fc2_b[d_out] | None)
+
+`config.indices_` carries the k routing-id vectors out of band and `config.stage` selects the MoE
+layer; backward returns gradients shaped like the inputs and decrements `config.stage`.
+
+Differences from the reference, all deliberate:
+  * the expert math runs through `config.backend` (hexa_moe_b200.ops: the sm_100a kernels behind
+    the C ABI; there is no CPU path) on the merged, 128-row-aligned segmentation of all k routes,
+    with bias, activation and activation derivative fused into the ESMM epilogues and no
+    transposed weight copies;
+  * ESTMM / ESS follow the operator definition (the reference kernels drop/duplicate 16-row chunks);
+  * data-centric expert gradients are reduce-scattered (AVG) along the hidden dimension instead of
+    all-reduced at full size and sliced (layers.py:431-474) - the same values, 1/W of the traffic;
+  * model-centric token gradients are reduce-scattered over the token dimension; the reference
+    sends its local slice to every destination (layers.py:392-396).
+"""
+from __future__ import annotations
+
+from typing import Any, List, Optional
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from . import losses
+
+
+# ------------------------------------------------------------------------------------------------
+# small collective helpers that work with both NCCL (GPU) and gloo (CPU tests)
+# ------------------------------------------------------------------------------------------------
+def _world(group) -> int:
+    return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+
+
+def _is_nccl(group) -> bool:
+    return dist.get_backend(group) == "nccl"
+
+
+def all_reduce_avg(t: Tensor, group) -> Tensor:
+    """In-place mean over ranks (gloo has no AVG)."""
+    if _world(group) == 1:
+        return t
+    if _is_nccl(group):
+        dist.all_reduce(t, op=dist.ReduceOp.AVG, group=group)
+    else:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+        t.div_(_world(group))
+    return t
+
+
+def reduce_scatter_hidden_avg(full: Tensor, split: List[int], rank: int, group) -> Tensor:
+    """Mean over ranks of `full` [E, H, ...], returning this rank's hidden slice [E, split[rank], ...].
+
+    NCCL: one reduce_scatter_tensor over slices padded to the largest one.  gloo: all-reduce + slice."""
+    W = len(split)
+    lo = sum(split[:rank])
+    if W == 1:
+        return full
+    if not _is_nccl(group):
+        red = all_reduce_avg(full.contiguous(), group)
+        return red[:, lo: lo + split[rank]]
+    bound = max(split)
+    E = full.shape[0]
+    packed = full.new_zeros((W, E, bound) + tuple(full.shape[2:]))
+    off = 0
+    for r, n in enumerate(split):
+        packed[r, :, :n].copy_(full[:, off: off + n])
+        off += n
+    out = full.new_empty((E, bound) + tuple(full.shape[2:]))
+    dist.reduce_scatter_tensor(out, packed, op=dist.ReduceOp.AVG, group=group)
+    return out[:, : split[rank]]
+
+
+def all_gather_tokens(t: Tensor, sizes: List[int], group) -> Tensor:
+    """Concatenate every rank's rows ([sizes[r], ...] on rank r) in rank order."""
+    W = len(sizes)
+    if W == 1:
+        return t
+    bound = max(sizes)
+    if all(s == bound for s in sizes):
+        out = t.new_empty((W * bound,) + tuple(t.shape[1:]))
+        dist.all_gather_into_tensor(out, t.contiguous(), group=group)
+        return out
+    padded = t.new_zeros((bound,) + tuple(t.shape[1:]))
+    padded[: t.shape[0]].copy_(t)
+    buf = t.new_empty((W, bound) + tuple(t.shape[1:]))
+    dist.all_gather_into_tensor(buf.view((W * bound,) + tuple(t.shape[1:])), padded, group=group)
+    return torch.cat([buf[r, : sizes[r]] for r in range(W)], dim=0)
+
+
+def reduce_scatter_tokens_sum(t: Tensor, sizes: List[int], rank: int, group) -> Tensor:
+    """Sum over ranks of `t` [sum(sizes), ...], returning this rank's token chunk."""
+    W = len(sizes)
+    if W == 1:
+        return t
+    lo = sum(sizes[:rank])
+    bound = max(sizes)
+    if _is_nccl(group) and all(s == bound for s in sizes):
+        out = t.new_empty((bound,) + tuple(t.shape[1:]))
+        dist.reduce_scatter_tensor(out, t.contiguous(), op=dist.ReduceOp.SUM, group=group)
+        return out
+    red = t.contiguous()
+    dist.all_reduce(red, op=dist.ReduceOp.SUM, group=group)
+    return red[lo: lo + sizes[rank]].contiguous()
+
+
+def gather_token_counts(n: int, device, group) -> List[int]:
+    """Token count of every rank (the reference uses all_gather_object, layers.py:132)."""
+    W = _world(group)
+    if W == 1:
+        return [n]
+    mine = torch.tensor([n], dtype=torch.int64, device=device)
+    out = torch.empty(W, dtype=torch.int64, device=device)
+    dist.all_gather_into_tensor(out, mine, group=group)
+    return [int(v) for v in out.tolist()]
+
+
+# ------------------------------------------------------------------------------------------------
+# routing glue
+# ------------------------------------------------------------------------------------------------
+def simplified_extract_critical(scores, top_k, loss_fn=losses.gshard_loss):
+    """top-k expert ids as a list of k vectors, plus the auxiliary loss (reference layers.py:480-489)."""
+    num_global_experts = int(scores.size(1))
+    top_k = min(top_k, num_global_experts)
+    topk_indices = torch.topk(scores, top_k, dim=1).indices
+    indices_s = [col.view(-1) for col in topk_indices.chunk(top_k, dim=1)]
+    l_loss = loss_fn(scores, topk_indices) if loss_fn is not None else None
+    return indices_s, l_loss
+
+
+def _stack_ids(indices_: List[Tensor], device) -> Tensor:
+    """k int vectors [T] -> one int32 [k, T] tensor (route-major, what the routing kernel reads)."""
+    return torch.stack([i.reshape(-1).to(device=device, dtype=torch.int32) for i in indices_], dim=0).contiguous()
+
+
+def _cast(w: Optional[Tensor], dtype) -> Optional[Tensor]:
+    if w is None:
+        return None
+    return w if w.dtype == dtype else w.to(dtype)
+
+
+# ------------------------------------------------------------------------------------------------
+# dense FFN (plain PyTorch; the layers either side of every MoE layer)
+# ------------------------------------------------------------------------------------------------
+class MLP_Implement(torch.autograd.Function):
+    """y = act(x fc1_w^T + b1) fc2_w + b2 with fc1_w [H,d], fc2_w [H,d_out]; weight and bias gradients are
+    averaged over the data-parallel ranks inside backward (reference layers.py:18-88)."""
+
+    @staticmethod
+    def forward(ctx: Any, config: Any, tokens_input: Tensor, fc1_w, fc2_w, fc1_bias, fc2_bias):
+        ctx.config = config
+        assert tokens_input.shape[1] == fc1_w.shape[1] and fc1_w.shape[0] == fc2_w.shape[0]
+        dtype = tokens_input.dtype
+        hid = tokens_input @ fc1_w.to(dtype).t()
+        if fc1_bias is not None:
+            hid = hid + fc1_bias.to(dtype)
+        ctx.save_for_backward(tokens_input, hid, fc1_w, fc2_w)
+        ctx.has_b1, ctx.has_b2 = fc1_bias is not None, fc2_bias is not None
+        y = config.activation_fn(hid) @ fc2_w.to(dtype)
+        if fc2_bias is not None:
+            y = y + fc2_bias.to(dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx: Any, dy: Tensor):
+        x, hid, fc1_w, fc2_w = ctx.saved_tensors
+        cfg = ctx.config
+        with torch.enable_grad():
+            hh = hid.detach().requires_grad_(True)
+            act = cfg.activation_fn(hh)
+            (dact,) = torch.autograd.grad(act.sum(), hh)
+        act = act.detach()
+        dtype = dy.dtype
+        d_act = dy @ fc2_w.to(dtype).t()
+        dw2 = (act.t() @ dy).to(fc2_w.dtype)
+        db2 = dy.sum(0).to(fc2_w.dtype) if ctx.has_b2 else None
+        d_hid = d_act * dact
+        dx = d_hid @ fc1_w.to(dtype)
+        dw1 = (d_hid.t() @ x).to(fc1_w.dtype)
+        db1 = d_hid.sum(0).to(fc1_w.dtype) if ctx.has_b1 else None
+        for g in (dw2, db2, dw1, db1):
+            if g is not None:
+                all_reduce_avg(g, cfg.group)
+        return None, dx, dw1, dw2, db1, db2
+
+
+# ------------------------------------------------------------------------------------------------
+# the MoE layer
+# ------------------------------------------------------------------------------------------------
+class FusedMoE_Shared_CudaCore(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx: Any, config: Any, tokens_input: Tensor, fc1_w, fc2_w, fc1_bias, fc2_bias):
+        cfg = config
+        ctx.config = cfg
+        stage = cfg.stage
+        ctx.stage = stage
+        x = tokens_input.contiguous()
+        assert x.shape[1] == fc1_w.shape[2], "token width does not match fc1_w"
+        T = x.shape[0]
+        dtype = x.dtype
+        W, rank = cfg.world_size, cfg.local_rank
+        ids = _stack_ids(cfg.indices_, x.device)                              # [k, T]
+        ctx.has_b1, ctx.has_b2 = fc1_bias is not None, fc2_bias is not None
+        ctx.param_dtypes = (fc1_w.dtype, fc2_w.dtype,
+                            None if fc1_bias is None else fc1_bias.dtype, None if fc2_bias is None else fc2_bias.dtype)
+        need_state = any(ctx.needs_input_grad)
+
+        if cfg.data_centric:
+            if W > 1:
+                # full expert weights of this layer from the pipeline-shared cache; start fetching the next layer's
+                cfg.cache.prefetch(stage + 1)
+                w1, w2, b1 = cfg.cache.get(stage)
+            else:
+                w1, w2, b1 = fc1_w, fc2_w, fc1_bias
+            w1, w2 = _cast(w1.detach(), dtype), _cast(w2.detach(), dtype)
+            y, st = cfg.backend.moe_forward(x, ids, w1, w2, None if b1 is None else b1.detach(),
+                                            None if fc2_bias is None else fc2_bias.detach(), cfg.act_id,
+                                            act_fn=cfg.activation_fn, route_major=True, need_state=need_state)
+            if W > 1:
+                cfg.cache.release(stage)
+            ctx.sizes = None
+            ctx.local_w = (w1, w2) if W == 1 else None
+        else:
+            # model-centric: every rank sees all tokens and owns a slice of the hidden dimension
+            sizes = gather_token_counts(T, x.device, cfg.group)
+            x_all = all_gather_tokens(x, sizes, cfg.group)
+            ids_all = all_gather_tokens(ids.t().contiguous(), sizes, cfg.group).t().contiguous()   # [k, T_w]
+            loc = cfg.local_dim_list_all[rank][stage]
+            w1 = _cast(fc1_w.detach()[:, :loc], dtype)
+            w2 = _cast(fc2_w.detach()[:, :loc], dtype)
+            b1 = None if fc1_bias is None else fc1_bias.detach()[:, :loc]
+            b2 = fc2_bias.detach() if (fc2_bias is not None and rank == 0) else None       # bias enters the sum once
+            y_all, st = cfg.backend.moe_forward(x_all, ids_all, w1, w2, b1, b2, cfg.act_id, act_fn=cfg.activation_fn,
+                                                route_major=True, need_state=need_state)
+            y = reduce_scatter_tokens_sum(y_all, sizes, rank, cfg.group)
+            ctx.sizes = sizes
+            ctx.local_w = (w1, w2)
+        ctx.state = st
+        return y.reshape(T, -1)
+
+    @staticmethod
+    def backward(ctx: Any, j_tokens_output: Tensor):
+        cfg = ctx.config
+        stage = ctx.stage
+        st = ctx.state
+        W, rank = cfg.world_size, cfg.local_rank
+        dy = j_tokens_output.contiguous()
+        dtype = dy.dtype
+        w1_dt, w2_dt, b1_dt, b2_dt = ctx.param_dtypes
+        be = cfg.backend
+
+        if cfg.data_centric:
+            if W > 1:
+                cfg.cache.prefetch(stage - 1)
+                w1, w2, _ = cfg.cache.get(stage)
+                w1, w2 = _cast(w1.detach(), dtype), _cast(w2.detach(), dtype)
+            else:
+                w1, w2 = ctx.local_w
+            split = [cfg.local_dim_list_all[r][stage] for r in range(W)]
+            dh, dw2, db2 = be.moe_backward_fc2(st, dy, w2, cfg.act_id, has_b2=ctx.has_b2, grad_dtype=w2_dt)
+            pending = cfg.cache.reduce_async(dw2, db2, split, rank) if W > 1 else None   # overlaps the fc1 backward
+            dx, dw1, db1 = be.moe_backward_fc1(st, dh, w1, has_b1=ctx.has_b1, grad_dtype=w1_dt)
+            if W > 1:
+                cfg.cache.release(stage)
+                dw2, db2 = pending.wait()
+                dw1 = reduce_scatter_hidden_avg(dw1, split, rank, cfg.group)
+                if db1 is not None:
+                    db1 = reduce_scatter_hidden_avg(db1, split, rank, cfg.group)
+        else:
+            sizes = ctx.sizes
+            w1, w2 = ctx.local_w
+            dy_all = all_gather_tokens(dy, sizes, cfg.group)
+            dh, dw2, db2 = be.moe_backward_fc2(st, dy_all, w2, cfg.act_id, has_b2=ctx.has_b2, grad_dtype=w2_dt)
+            dx_all, dw1, db1 = be.moe_backward_fc1(st, dh, w1, has_b1=ctx.has_b1, grad_dtype=w1_dt)
+            dx = reduce_scatter_tokens_sum(dx_all, sizes, rank, cfg.group)
+            # gradients cover the local hidden slice only; pad up to the stored parameter width
+            bound = ctx.needs_pad = None
+        ctx.state = None
+        cfg.stage = stage - 1
+        if db1 is not None:
+            db1 = db1.to(b1_dt)
+        if db2 is not None:
+            db2 = db2.to(b2_dt)
+        return None, dx, dw1, dw2, db1, db2
