@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE-layer hot path (ESMM / ESTMM / ESS + routing) through the MoE_Cascaded API.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload ("c5-layer"): the d=2048 / hidden 8192 / 64 experts / top-2 bf16 MoE layer, GELU, both
+biases, `--tokens` tokens per GPU (default 131072) ~ N(0,1), two such layers cascaded in one
+MoE_Cascaded module so that the pipeline-shared cache has a next layer to prefetch.  A step is
+forward + backward of both layers; the metric counts tokens through one layer:
+value = tokens_per_gpu * n_gpus * layers / step_time.  With N > 1 the module runs in data-centric
+mode (tokens sharded over ranks, expert weights sharded along the hidden dimension, all-gathered
+per layer and their gradients reduce-scattered): weak scaling.
+
+Prints ONE JSON line (rank 0).  `value` is measured with inputs resident in HBM; `e2e` repeats the
+measurement with the step's input copied from pinned host memory and the loss read back to the
+host inside the timed region.  `roofline` is for the dominant kernel (the tcgen05 grouped GEMM),
+from CUDA events recorded around its launches during the timed steps.  `cpu_baseline` times the
+CPU oracle's restatement of the same layer on the host cores on a bounded sample.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+TOP_K, LAYERS = 2, 2
+WORKLOADS = {  # name -> (d_model, hidden, experts, default tokens per GPU)
+    "c5": (2048, 8192, 64, 131072),
+    "c2": (768, 3072, 32, 16384),
+    "small": (256, 1024, 8, 8192),
+}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the workload's)")
+    ap.add_argument("--workload", default="c5", choices=["c5", "c2", "small"],
+                    help="c5: the headline layer; c2: d=768/H=3072/E=32, 16384 tokens (operator-sweep config, sized for ncu "
+                         "captures); small: d=256/H=1024/E=8, 8192 tokens (smoke)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(tflops=float(p.get("bf16_tflops_sustained", p.get("bf16_tflops"))), hbm=float(p["hbm_gbs"]), source="measured")
+    return dict(tflops=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return None
+        sm.sort()
+        return dict(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline / reference arm: the oracle's fp32 restatement on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_setup(d, H, E_sample, k, tokens):
+    """Seeded synthetic inputs of one layer for the CPU pass (generated outside any timed region)."""
+    import torch
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(tokens, d, generator=g)
+    w1 = torch.randn(E_sample, H, d, generator=g) / d ** 0.5
+    w2 = torch.randn(E_sample, H, d, generator=g) / H ** 0.5
+    b1 = torch.randn(E_sample, H, generator=g) * 0.02
+    b2 = torch.randn(E_sample, d, generator=g) * 0.02
+    dy = torch.randn(tokens, d, generator=g)
+    ids = torch.topk(torch.randn(tokens, E_sample, generator=g), k, dim=1).indices.to(torch.int32)
+    return x, ids, w1, w2, b1, b2, dy
+
+
+def cpu_pass(data):
+    """One fwd+bwd of the layer with the CPU oracle's grouped-matmul restatement; returns seconds."""
+    from oracle import hexa_oracle as O
+    t0 = time.perf_counter()
+    O.moe_layer_fast(*data)
+    return time.perf_counter() - t0
+
+
+def cpu_sample_size(d, H, k, budget_s=15.0):
+    """Tokens that make one CPU pass last about budget_s, from a short probe."""
+    probe = cpu_setup(d, H, 8, k, 2048)
+    cpu_pass(probe)
+    rate = 2048 / cpu_pass(probe)
+    n = int(rate * budget_s)
+    return max(2048, min(n // 1024 * 1024, 65536))
+
+
+def run_reference(args):
+    """The reference has no CPU implementation of this path (its kernels are Triton / CUDA only), so this arm
+    times the CPU oracle port of the same layer on the host cores, on a bounded token sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    d, H, EXPERTS, _ = WORKLOADS[args.workload]
+    k = TOP_K
+    E_s = 8
+    n = cpu_sample_size(d, H, k, budget_s=8.0)
+    data = cpu_setup(d, H, E_s, k, n)
+    for _ in range(min(args.warmup, 1)):
+        cpu_pass(data)
+    dt = sum(cpu_pass(data) for _ in range(args.steps)) / args.steps
+    val = n / dt
+    cores = os.cpu_count() or 1
+    sample = f"{n} tokens top-{k} over {E_s} of the {EXPERTS} experts per step (same d, hidden, per-token work), fp32"
+    line = dict(metric="moe_layer_fwd_bwd_tokens_per_s", value=val, unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None,
+                dtype="f32", data="synthetic", impl="reference",
+                config=dict(workload=args.workload + "-layer", d_model=d, hidden=H, experts=EXPERTS,
+                            top_k=k, note="CPU oracle port: the reference ships no CPU path for these operators"),
+                cpu_baseline=dict(value=val, unit="tokens/s", cores=cores, kind="port", sample=sample),
+                e2e=dict(value=val, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n_gpus = world
+
+    from hexa_moe_b200 import build, ops
+    from hexa_moe import moe as hmoe
+    if rank == 0 and build.needs_build():
+        build.build()
+    if world > 1:
+        dist.barrier()
+
+    d, H, E, T_default = WORKLOADS[args.workload]
+    k, L = TOP_K, LAYERS
+    T = args.tokens or T_default
+    torch.manual_seed(0)
+    m = hmoe.MoE_Cascaded(gate_type={'type': 'top', 'k': k, 'fp32_gate': True}, model_dim_list=[d] * L,
+                          moe_idx_list=list(range(L)), mlp_ratio=H // d, mlp_proportion=None, num_global_experts=E,
+                          total_depth=L, data_centric=True, mlp_fc1_bias=True, mlp_fc2_bias=True,
+                          activation_fn=lambda t: F.gelu(t))
+    with torch.no_grad():   # random-init weights at a scale that keeps activations O(1)
+        for name, p in m.named_parameters():
+            if name.startswith("batched_fc1_w"):
+                p.normal_(0, d ** -0.5)
+            elif name.startswith("batched_fc2_w"):
+                p.normal_(0, H ** -0.5)
+            elif "bias" in name:
+                p.normal_(0, 0.02)
+    m = m.to(torch.bfloat16).to(dev).train()
+    for g in m.gates:
+        g.gate_noise = 0.0
+    params = [p for p in m.parameters()]
+
+    gen = torch.Generator().manual_seed(1234 + rank)
+    x_host = torch.randn(T, d, generator=gen).to(torch.bfloat16).pin_memory()
+    x_dev = x_host.to(dev)
+    x_stage = torch.empty_like(x_dev)
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def step(x):
+        for p in params:
+            p.grad = None
+        h = x.detach().requires_grad_(True)
+        aux = 0
+        for i in range(L):
+            h, l = m(i, h)
+            aux = aux + l
+        loss = h.float().pow(2).mean() + 0.01 * aux
+        loss.backward()
+        return loss
+
+    def step_resident():
+        return step(x_dev)
+
+    def step_e2e():
+        x_stage.copy_(x_host, non_blocking=True)
+        loss = step(x_stage)
+        loss_host.copy_(loss.detach(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return float(loss_host)
+
+    def timed(fn, n):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t)
+            dist.barrier()
+        return ms / n
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches0 = ops.LAUNCHES
+    ops.PROFILE = []
+    ms = timed(step_resident, args.steps)
+    prof, ops.PROFILE = ops.PROFILE, None
+    launches = ops.LAUNCHES - launches0
+    clocks = sampler.stop() if sampler else None
+
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+
+    # ---- per-kernel summary from the events recorded during the timed steps ----
+    per = {}
+    for name, e0, e1, work in prof:
+        t_ms = e0.elapsed_time(e1)
+        s = per.setdefault(name.split(":")[0], [0, 0.0, 0.0])
+        s[0] += 1; s[1] += t_ms; s[2] += work
+    pk = peaks()
+    gemm_n = per.get("esmm", [0, 0, 0])[0] + per.get("estmm", [0, 0, 0])[0]
+    gemm_ms = per.get("esmm", [0, 0, 0])[1] + per.get("estmm", [0, 0, 0])[1]
+    gemm_fl = per.get("esmm", [0, 0, 0])[2] + per.get("estmm", [0, 0, 0])[2]
+    achieved = gemm_fl / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    roofline = dict(bound="tensor", kernel="gemm_tc_kernel (ESMM + ESTMM launches)", achieved=achieved, peak=pk["tflops"],
+                    unit="TFLOP/s", frac=achieved / pk["tflops"], peak_source=pk["source"] + " (sustained cuBLAS bf16)",
+                    launches=gemm_n, avg_launch_ms=gemm_ms / max(gemm_n, 1), flops_per_launch=gemm_fl / max(gemm_n, 1),
+                    traffic=None)
+    kernels = {n_: dict(calls=v[0], ms_total=round(v[1], 3)) for n_, v in per.items()}
+
+    tokens_per_step = T * n_gpus * L
+    value = tokens_per_step / (ms * 1e-3)
+    e2e_value = tokens_per_step / (ms_e2e * 1e-3)
+    layer_flops = 12.0 * T * k * d * H * L
+    cpu_baseline = None
+    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
+        n_s = cpu_sample_size(d, H, k, budget_s=15.0)
+        secs = cpu_pass(cpu_setup(d, H, 8, k, n_s))
+        rate = n_s / secs
+        cpu_baseline = dict(value=rate, unit="tokens/s", cores=os.cpu_count() or 1, kind="port", seconds=round(secs, 2),
+                            sample=f"{n_s} tokens top-{k} over 8 of the {E} experts (same d, hidden and per-token work), fp32, one pass")
+    if rank == 0:
+        line = dict(metric="moe_layer_fwd_bwd_tokens_per_s", value=value, unit="tokens/s", n_gpus=n_gpus, steps=args.steps,
+                    warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
+                    dtype="bf16", data="synthetic",
+                    config=dict(workload=args.workload + "-layer", d_model=d, hidden=H, experts=E,
+                                top_k=k, layers=L, tokens_per_gpu=T, activation="gelu", mode="data-centric",
+                                l2="inputs larger than L2 (expert weights %.1f GB per layer)" % (2 * E * H * d * 2 / 1e9)),
+                    model_tflops_per_gpu=layer_flops / (ms * 1e-3) / 1e12,
+                    e2e=dict(value=e2e_value, unit="tokens/s", ms_per_step=ms_e2e, h2d_bytes_per_step=x_host.numel() * 2,
+                             d2h_bytes_per_step=4),
+                    gpu_launches=launches, kernels=kernels, roofline=roofline, cpu_baseline=cpu_baseline, clocks=clocks)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -182,6 +182,43 @@ __device__ __forceinline__ float unpack_hi(uint32_t w, int is_bf16) {
   return __half2float(__ushort_as_half((unsigned short)(w >> 16)));
 }
 
+// Epilogue of one 32-column chunk of one row: f holds acc + bias.  Writes `ncols` (a multiple of 8) columns.
+//   EPI_ACT    aux (if given) <- f ; c <- act(f)        EPI_DACT   c <- f * act'(aux)        EPI_LINEAR   c <- f
+// Rows that are not live (segment padding) are written as zeros.
+template <int EPI, int ACT>
+__device__ __forceinline__ void store_chunk(const float (&f)[32], uint16_t* cp, uint16_t* xp, int ncols, bool live, int is_bf16) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    if (g * 8 >= ncols) break;
+    uint4 w;
+    uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
+    if (EPI == HEXA_EPI_ACT) {
+      if (xp) {
+        uint4 y;
+        uint32_t* yp = reinterpret_cast<uint32_t*>(&y);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) yp[i] = live ? pack2(f[8 * g + 2 * i], f[8 * g + 2 * i + 1], is_bf16) : 0u;
+        *reinterpret_cast<uint4*>(xp + g * 8) = y;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        wp[i] = live ? pack2(act_fast<ACT>(f[8 * g + 2 * i]), act_fast<ACT>(f[8 * g + 2 * i + 1]), is_bf16) : 0u;
+    } else if (EPI == HEXA_EPI_DACT) {
+      const uint4 y = *reinterpret_cast<const uint4*>(xp + g * 8);
+      const uint32_t* yp = reinterpret_cast<const uint32_t*>(&y);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        wp[i] = live ? pack2(f[8 * g + 2 * i] * act_grad_fast<ACT>(unpack_lo(yp[i], is_bf16)),
+                             f[8 * g + 2 * i + 1] * act_grad_fast<ACT>(unpack_hi(yp[i], is_bf16)), is_bf16)
+                     : 0u;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) wp[i] = live ? pack2(f[8 * g + 2 * i], f[8 * g + 2 * i + 1], is_bf16) : 0u;
+    }
+    *reinterpret_cast<uint4*>(cp + g * 8) = w;
+  }
+}
+
 template <int BN> struct Cfg {
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr uint32_t kBBytes = BN * BLOCK_K * 2;
@@ -422,35 +459,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           uint16_t* cp = reinterpret_cast<uint16_t*>(p.c) + r * p.ldc + gcol;
           uint16_t* xp = p.aux ? reinterpret_cast<uint16_t*>(p.aux) + r * p.ldaux + gcol : nullptr;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (gcol + g * 8 >= p.n) break;
-            uint4 w;
-            uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
-            if (p.epilogue == HEXA_EPI_ACT) {
-              if (xp) {
-                uint4 y;
-                uint32_t* yp = reinterpret_cast<uint32_t*>(&y);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) yp[i] = live ? pack2(f[8 * g + 2 * i], f[8 * g + 2 * i + 1], is_bf16) : 0u;
-                *reinterpret_cast<uint4*>(xp + g * 8) = y;
-              }
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                wp[i] = live ? pack2(act_apply(p.act, f[8 * g + 2 * i]), act_apply(p.act, f[8 * g + 2 * i + 1]), is_bf16) : 0u;
-            } else if (p.epilogue == HEXA_EPI_DACT) {
-              const uint4 y = *reinterpret_cast<const uint4*>(xp + g * 8);
-              const uint32_t* yp = reinterpret_cast<const uint32_t*>(&y);
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                wp[i] = live ? pack2(f[8 * g + 2 * i] * act_grad(p.act, unpack_lo(yp[i], is_bf16)),
-                                     f[8 * g + 2 * i + 1] * act_grad(p.act, unpack_hi(yp[i], is_bf16)), is_bf16)
-                             : 0u;
-            } else {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) wp[i] = live ? pack2(f[8 * g + 2 * i], f[8 * g + 2 * i + 1], is_bf16) : 0u;
-            }
-            *reinterpret_cast<uint4*>(cp + g * 8) = w;
+          const int ncols = (int)min((int64_t)32, p.n - gcol);
+          switch (p.epilogue * 8 + p.act) {
+            case HEXA_EPI_ACT * 8 + HEXA_ACT_RELU: store_chunk<HEXA_EPI_ACT, HEXA_ACT_RELU>(f, cp, xp, ncols, live, is_bf16); break;
+            case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU: store_chunk<HEXA_EPI_ACT, HEXA_ACT_GELU>(f, cp, xp, ncols, live, is_bf16); break;
+            case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU_TANH: store_chunk<HEXA_EPI_ACT, HEXA_ACT_GELU_TANH>(f, cp, xp, ncols, live, is_bf16); break;
+            case HEXA_EPI_ACT * 8 + HEXA_ACT_SILU: store_chunk<HEXA_EPI_ACT, HEXA_ACT_SILU>(f, cp, xp, ncols, live, is_bf16); break;
+            case HEXA_EPI_ACT * 8 + HEXA_ACT_NONE: store_chunk<HEXA_EPI_ACT, HEXA_ACT_NONE>(f, cp, xp, ncols, live, is_bf16); break;
+            case HEXA_EPI_DACT * 8 + HEXA_ACT_RELU: store_chunk<HEXA_EPI_DACT, HEXA_ACT_RELU>(f, cp, xp, ncols, live, is_bf16); break;
+            case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU: store_chunk<HEXA_EPI_DACT, HEXA_ACT_GELU>(f, cp, xp, ncols, live, is_bf16); break;
+            case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU_TANH: store_chunk<HEXA_EPI_DACT, HEXA_ACT_GELU_TANH>(f, cp, xp, ncols, live, is_bf16); break;
+            case HEXA_EPI_DACT * 8 + HEXA_ACT_SILU: store_chunk<HEXA_EPI_DACT, HEXA_ACT_SILU>(f, cp, xp, ncols, live, is_bf16); break;
+            default: store_chunk<HEXA_EPI_LINEAR, HEXA_ACT_NONE>(f, cp, xp, ncols, live, is_bf16); break;
           }
         }
       }

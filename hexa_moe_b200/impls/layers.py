@@ -280,8 +280,6 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
             dh, dw2, db2 = be.moe_backward_fc2(st, dy_all, w2, cfg.act_id, has_b2=ctx.has_b2, grad_dtype=w2_dt)
             dx_all, dw1, db1 = be.moe_backward_fc1(st, dh, w1, has_b1=ctx.has_b1, grad_dtype=w1_dt)
             dx = reduce_scatter_tokens_sum(dx_all, sizes, rank, cfg.group)
-            # gradients cover the local hidden slice only; pad up to the stored parameter width
-            bound = ctx.needs_pad = None
         ctx.state = None
         cfg.stage = stage - 1
         if db1 is not None:

@@ -16,6 +16,36 @@ from . import _lib as L
 from ._lib import check, dt, lib, ptr, stream_of
 
 
+# ---- optional per-call instrumentation (used by bench.py; off by default) --------------------------
+# LAUNCHES counts kernels launched through the C ABI.  When PROFILE is a list, every wrapper appends
+# (name, start_event, end_event, algorithmic_work) with CUDA events recorded on the launching stream.
+LAUNCHES = 0
+PROFILE = None
+_KERNELS_PER_CALL = dict(route=3, gather=1, combine=1, esmm=1, estmm=1, ess=2, mask=1)
+
+
+class _Timed:
+    __slots__ = ("name", "work", "ev")
+
+    def __init__(self, name, work=0.0):
+        self.name, self.work, self.ev = name, work, None
+
+    def __enter__(self):
+        global LAUNCHES
+        LAUNCHES += _KERNELS_PER_CALL[self.name.split(":")[0]]
+        if PROFILE is not None:
+            self.ev = torch.cuda.Event(enable_timing=True)
+            self.ev.record()
+        return self
+
+    def __exit__(self, *exc):
+        if self.ev is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            PROFILE.append((self.name, self.ev, end, self.work))
+        return False
+
+
 @dataclass
 class Routing:
     """Device-side result of `route` (all int32 tensors) plus the static sizes."""
@@ -55,8 +85,9 @@ def route(ids: torch.Tensor, num_experts: int, align: int = L.ROW_TILE, route_ma
                 T, k, num_experts, align, cap)
     ws_bytes = lib().hexa_route_workspace_bytes(T, k, num_experts)
     ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
-    check(lib().hexa_route(ptr(ids), T, k, st, sk, num_experts, align, ptr(r.counts), ptr(r.seg_offsets), ptr(r.pad_offsets),
-                           ptr(r.row_token), ptr(r.token_row), ptr(r.tile_expert), ptr(ws), ws.numel(), s), "hexa_route")
+    with _Timed("route", 12.0 * T * k):
+        check(lib().hexa_route(ptr(ids), T, k, st, sk, num_experts, align, ptr(r.counts), ptr(r.seg_offsets), ptr(r.pad_offsets),
+                               ptr(r.row_token), ptr(r.token_row), ptr(r.tile_expert), ptr(ws), ws.numel(), s), "hexa_route")
     return r
 
 
@@ -71,8 +102,9 @@ def gather_rows(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = Non
     cols = src.shape[1]
     if out is None:
         out = torch.empty(r.row_capacity, cols, dtype=src.dtype, device=src.device)
-    check(lib().hexa_gather_rows(ptr(src), _ld(src), ptr(r.row_token), ptr(r.pad_offsets), r.num_experts, r.row_capacity,
-                                 cols, ptr(out), _ld(out), dt(src), stream_of(src)), "hexa_gather_rows")
+    with _Timed("gather", 2.0 * r.num_tokens * r.top_k * cols * src.element_size()):
+        check(lib().hexa_gather_rows(ptr(src), _ld(src), ptr(r.row_token), ptr(r.pad_offsets), r.num_experts, r.row_capacity,
+                                     cols, ptr(out), _ld(out), dt(src), stream_of(src)), "hexa_gather_rows")
     return out
 
 
@@ -81,8 +113,9 @@ def combine_rows(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = No
     cols = src.shape[1]
     if out is None:
         out = torch.empty(r.num_tokens, cols, dtype=src.dtype, device=src.device)
-    check(lib().hexa_combine_rows(ptr(src), _ld(src), ptr(r.token_row), r.num_tokens, r.top_k, cols, ptr(out), _ld(out),
-                                  dt(src), stream_of(src)), "hexa_combine_rows")
+    with _Timed("combine", (r.top_k + 1.0) * r.num_tokens * cols * src.element_size()):
+        check(lib().hexa_combine_rows(ptr(src), _ld(src), ptr(r.token_row), r.num_tokens, r.top_k, cols, ptr(out), _ld(out),
+                                      dt(src), stream_of(src)), "hexa_combine_rows")
     return out
 
 
@@ -108,10 +141,11 @@ def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Opti
         raise L.HexaError("esmm: bias must be float32")
     if out is None:
         out = torch.empty(r.row_capacity, n_out, dtype=a.dtype, device=a.device)
-    check(lib().hexa_esmm(ptr(a), _ld(a), ptr(b), b_layout, b.stride(1), b.stride(0), ptr(bias),
-                          0 if bias is None else _ld(bias), ptr(aux), 0 if aux is None else _ld(aux), ptr(out), _ld(out),
-                          ptr(r.tile_expert), ptr(r.pad_offsets), ptr(r.row_token), r.num_experts, r.row_capacity, n_out, k,
-                          dt(a), epilogue, act, engine, stream_of(a)), "hexa_esmm")
+    with _Timed("esmm:%d" % epilogue, 2.0 * r.num_tokens * r.top_k * n_out * k):
+        check(lib().hexa_esmm(ptr(a), _ld(a), ptr(b), b_layout, b.stride(1), b.stride(0), ptr(bias),
+                              0 if bias is None else _ld(bias), ptr(aux), 0 if aux is None else _ld(aux), ptr(out), _ld(out),
+                              ptr(r.tile_expert), ptr(r.pad_offsets), ptr(r.row_token), r.num_experts, r.row_capacity, n_out, k,
+                              dt(a), epilogue, act, engine, stream_of(a)), "hexa_esmm")
     return out
 
 
@@ -130,8 +164,9 @@ def estmm(p: torch.Tensor, q: torch.Tensor, r: Routing, out_dtype: Optional[torc
             raise L.HexaError("estmm: beta=1 needs an existing out")
     if out.stride(2) != 1:
         raise L.HexaError("estmm: out must have unit inner stride")
-    check(lib().hexa_estmm(ptr(p), _ld(p), ptr(q), _ld(q), ptr(r.pad_offsets), r.num_experts, r.row_capacity, m, n, ptr(out),
-                           out.stride(1), out.stride(0), dt(p), dt(out), beta, engine, stream_of(p)), "hexa_estmm")
+    with _Timed("estmm", 2.0 * r.num_tokens * r.top_k * m * n):
+        check(lib().hexa_estmm(ptr(p), _ld(p), ptr(q), _ld(q), ptr(r.pad_offsets), r.num_experts, r.row_capacity, m, n, ptr(out),
+                               out.stride(1), out.stride(0), dt(p), dt(out), beta, engine, stream_of(p)), "hexa_estmm")
     return out
 
 
@@ -144,14 +179,16 @@ def ess(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = None) -> to
         out = torch.empty(r.num_experts, cols, dtype=torch.float32, device=src.device)
     nbytes = lib().hexa_ess_workspace_bytes(r.row_capacity, cols)
     ws = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=src.device)
-    check(lib().hexa_ess(ptr(src), _ld(src), ptr(r.pad_offsets), r.num_experts, r.row_capacity, cols, ptr(out), _ld(out),
-                         dt(src), ptr(ws), ws.numel(), stream_of(src)), "hexa_ess")
+    with _Timed("ess", 1.0 * r.num_tokens * r.top_k * cols * src.element_size()):
+        check(lib().hexa_ess(ptr(src), _ld(src), ptr(r.pad_offsets), r.num_experts, r.row_capacity, cols, ptr(out), _ld(out),
+                             dt(src), ptr(ws), ws.numel(), stream_of(src)), "hexa_ess")
     return out
 
 
 def mask_pad_rows(buf: torch.Tensor, r: Routing) -> torch.Tensor:
-    check(lib().hexa_mask_pad_rows(ptr(buf), _ld(buf), ptr(r.row_token), ptr(r.pad_offsets), r.num_experts, r.row_capacity,
-                                   buf.shape[1], dt(buf), stream_of(buf)), "hexa_mask_pad_rows")
+    with _Timed("mask"):
+        check(lib().hexa_mask_pad_rows(ptr(buf), _ld(buf), ptr(r.row_token), ptr(r.pad_offsets), r.num_experts, r.row_capacity,
+                                       buf.shape[1], dt(buf), stream_of(buf)), "hexa_mask_pad_rows")
     return buf
 
 
@@ -203,10 +240,9 @@ def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=Fa
     return y, (LayerState(r, xs, y1, h, g) if need_state else None)
 
 
-def moe_backward(st: LayerState, dy, w1, w2, act_id: int, has_b1=True, has_b2=True, grad_dtype=None,
-                 engine=L.ENGINE_AUTO):
-    """Gradients of moe_forward.  Returns (dx [T,d], dw1 [E,H,d], dw2 [E,H,d_out], db1 [E,H] | None,
-    db2 [E,d_out] | None); bias gradients are float32, weight gradients `grad_dtype` (default: dtype of dy)."""
+def moe_backward_fc2(st: LayerState, dy, w2, act_id: int, has_b2=True, grad_dtype=None, engine=L.ENGINE_AUTO):
+    """First half of the layer backward: (dh [cap,H] = dy W2^T * act'(y1), dw2 [E,H,d_out], db2 [E,d_out] | None).
+    Split from the fc1 half so a caller can start reducing dw2/db2 across ranks while fc1 runs."""
     r = st.routing
     dys = gather_rows(dy.contiguous(), r)
     db2 = ess(dys, r) if has_b2 else None
@@ -217,8 +253,23 @@ def moe_backward(st: LayerState, dy, w1, w2, act_id: int, has_b1=True, has_b2=Tr
         dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_LINEAR, engine=engine)
         dh.mul_(st.act_grad)
         mask_pad_rows(dh, r)
+    return dh, dw2, db2
+
+
+def moe_backward_fc1(st: LayerState, dh, w1, has_b1=True, grad_dtype=None, engine=L.ENGINE_AUTO):
+    """Second half: (dx [T,d], dw1 [E,H,d], db1 [E,H] | None) from dh."""
+    r = st.routing
     db1 = ess(dh, r) if has_b1 else None
     dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine)
     dxs = esmm(dh, w1, L.B_KN, r, None, L.EPI_LINEAR, engine=engine)
     dx = combine_rows(dxs, r)
+    return dx, dw1, db1
+
+
+def moe_backward(st: LayerState, dy, w1, w2, act_id: int, has_b1=True, has_b2=True, grad_dtype=None,
+                 engine=L.ENGINE_AUTO):
+    """Gradients of moe_forward.  Returns (dx [T,d], dw1 [E,H,d], dw2 [E,H,d_out], db1 [E,H] | None,
+    db2 [E,d_out] | None); bias gradients are float32, weight gradients `grad_dtype` (default: dtype of dy)."""
+    dh, dw2, db2 = moe_backward_fc2(st, dy, w2, act_id, has_b2, grad_dtype, engine)
+    dx, dw1, db1 = moe_backward_fc1(st, dh, w1, has_b1, grad_dtype, engine)
     return dx, dw1, dw2, db1, db2

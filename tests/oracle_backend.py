@@ -1,0 +1,40 @@
+"""Test double for `config.backend`: the CPU oracle behind the interface of hexa_moe_b200.ops.
+
+Only tests use it - to exercise the multi-rank host logic (sharding, gathers, reductions) on
+CPU `gloo` ranks, where the CUDA kernels cannot run.  The product never imports this file.
+"""
+import torch
+
+from oracle import hexa_oracle as O
+
+
+class _State:
+    pass
+
+
+def moe_forward(x, ids, w1, w2, b1, b2, act_id, act_fn=None, route_major=False, engine=0, need_state=True):
+    ids_tk = ids.t().contiguous() if route_major else ids
+    st = _State()
+    st.x, st.ids, st.w1, st.w2, st.b1, st.b2, st.act = x, ids_tk, w1, w2, b1, b2, act_fn
+    res = O.moe_layer(x, ids_tk, w1, w2, b1, b2, act_fn)
+    return res["y"].to(x.dtype), st
+
+
+def _full(st, dy):
+    if not hasattr(st, "res"):
+        b2 = st.b2 if st.b2 is not None else torch.zeros(st.w2.shape[0], st.w2.shape[2])
+        b1 = st.b1 if st.b1 is not None else torch.zeros(st.w1.shape[0], st.w1.shape[1])
+        st.res = O.moe_layer(st.x, st.ids, st.w1, st.w2, b1, b2, st.act, dy)
+    return st.res
+
+
+def moe_backward_fc2(st, dy, w2, act_id, has_b2=True, grad_dtype=None, engine=0):
+    r = _full(st, dy)
+    gd = grad_dtype or dy.dtype
+    return None, r["dw2"].to(gd), (r["db2"].float() if has_b2 else None)
+
+
+def moe_backward_fc1(st, dh, w1, has_b1=True, grad_dtype=None, engine=0):
+    r = st.res
+    gd = grad_dtype or st.x.dtype
+    return r["dx"].to(st.x.dtype), r["dw1"].to(gd), (r["db1"].float() if has_b1 else None)

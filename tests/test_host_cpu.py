@@ -1,0 +1,136 @@
+"""Host-side logic that needs no GPU: the C ABI loads and exports what the header declares, the
+module mirrors the reference's constructor / parameter names / sharding rule, activation
+recognition, and loud failure where there is no CUDA device."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _build():
+    from hexa_moe_b200 import build
+    return build.build()
+
+
+def test_library_exports_every_declared_symbol():
+    lib_path = _build()
+    hdr = open(os.path.join(ROOT, "include", "hexa_moe_b200.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    declared = sorted(set(re.findall(r"\b(hexa_[a-z0-9_]+)\s*\(", hdr)))
+    assert len(declared) >= 12
+    lib = ctypes.CDLL(lib_path)
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/hexa_moe_b200.h but not exported"
+    from hexa_moe_b200 import _lib
+    assert set(_lib.SIGNATURES) == set(declared)
+    # pure host entry points can be called without a GPU
+    h = _lib.lib()
+    assert h.hexa_version() >= 100
+    assert h.hexa_route_row_capacity(1000, 2, 8, 128) == (2000 + 8 * 127 + 127) // 128 * 128
+    assert h.hexa_route_workspace_bytes(1000, 2, 8) == 4 * 8 * 4
+    assert h.hexa_ess_workspace_bytes(1024, 100) == 8 * 100 * 4
+    assert h.hexa_route_row_capacity(10, 0, 8, 128) == -1
+
+
+def test_argument_errors_come_back_as_status_codes():
+    from hexa_moe_b200 import _lib
+    h = _lib.lib()
+    rc = h.hexa_route(None, 10, 1, 1, 10, 4, 128, None, None, None, None, None, None, None, 0, None)
+    assert rc == -1 and b"null" in h.hexa_last_error_string()
+    rc = h.hexa_esmm(None, 0, None, 0, 0, 0, None, 0, None, 0, None, 0, None, None, None, 4, 128, 8, 8, 2, 0, 0, 0, None)
+    assert rc == -1
+
+
+def _toy(**kw):
+    from hexa_moe import moe as hmoe
+    args = dict(gate_type={'type': 'top', 'k': 1, 'gate_noise': 1.0, 'fp32_gate': True}, model_dim_list=[32] * 4,
+                moe_idx_list=[2, 3], mlp_ratio=4, mlp_proportion=None, num_global_experts=4, total_depth=4,
+                data_centric=True, mlp_fc1_bias=True, mlp_fc2_bias=True, activation_fn=lambda t: F.gelu(t))
+    args.update(kw)
+    return hmoe.MoE_Cascaded(**args)
+
+
+def test_module_parameters_match_reference_state_dict(golden_dir):
+    z = np.load(os.path.join(golden_dir, "module.npz"))
+    ref = {n.split("param/")[1]: z[n] for n in z.files if n.startswith("top1/param/")}
+    m = _toy()
+    mine = {n: tuple(p.shape) for n, p in m.state_dict().items()}
+    assert mine == {n: v.shape for n, v in ref.items()}
+    m.load_state_dict({n: torch.from_numpy(v) for n, v in ref.items()})
+    # dense depths are plain PyTorch and match the reference's activations on CPU
+    x = torch.from_numpy(z["top1/x"])
+    y0, l0 = m(0, x)
+    np.testing.assert_allclose(y0.detach().numpy(), z["top1/y0"], rtol=2e-5, atol=2e-5)
+    assert l0 == 0
+    y1, _ = m(1, torch.from_numpy(z["top1/y0"]))
+    np.testing.assert_allclose(y1.detach().numpy(), z["top1/y1"], rtol=2e-5, atol=2e-5)
+
+
+def test_moe_depth_fails_loudly_without_cuda():
+    from hexa_moe_b200._lib import HexaError
+    m = _toy()
+    with pytest.raises(HexaError, match="CUDA tensors only"):
+        m(2, torch.randn(2, 8, 32))
+
+
+def test_init_and_options():
+    m = _toy(mlp_fc1_bias=False, gate_type=[{'type': 'top', 'k': 2}, {'type': 'cosine_top', 'k': 1, 'proj_dim': 16}])
+    assert m.batched_fc1_bias[0] is None and m.mlp_fc1_b[0] is None
+    assert len(m.gates) == 4 and m.gate_len == 2
+    assert type(m.gates[1]).__name__ == "CosineTopKGate" and type(m.gates[3]).__name__ == "CosineTopKGate"
+    assert abs(float(m.batched_fc1_w[0].detach().std()) - 0.005) < 5e-4 and float(m.batched_fc2_bias[0].detach().abs().max()) == 0
+    with pytest.raises(Exception, match="Unrecognized gate_type"):
+        _toy(gate_type={'type': 'nope', 'k': 1})
+    with pytest.raises(Exception, match="Unrecognized argument"):
+        _toy(gate_type={'type': 'top', 'k': 1, 'bogus': 3})
+    m2 = _toy(gate_type="Top2Gate")
+    assert m2.gates[0].top_k == 2
+    os.environ["SKIP_MOE"] = "1"
+    try:
+        m3 = _toy()
+        x = torch.randn(2, 4, 32)
+        y, l = m3(2, x)
+        assert y is x and l is None
+    finally:
+        del os.environ["SKIP_MOE"]
+
+
+def test_split_hidden_rule():
+    from hexa_moe_b200.impls.cascaded_moe import split_hidden
+    from oracle import hexa_oracle as O
+    for H, prop in ((8192, [0.2, 0.2, 0.15, 0.15, 0.1, 0.1, 0.05, 0.05]), (512, [0.5, 0.5]), (100, [1 / 3] * 3), (64, [1.0])):
+        assert split_hidden(H, prop) == O.dim_split(H, prop)
+    assert split_hidden(8192, [0.2, 0.2, 0.15, 0.15, 0.1, 0.1, 0.05, 0.05]) == [1639, 1639, 1229, 1229, 819, 819, 409, 409]
+
+
+def test_activation_recognition():
+    from hexa_moe_b200 import _lib as L
+    from hexa_moe_b200.impls.activations import classify
+    assert classify(lambda t: F.gelu(t)) == L.ACT_GELU
+    assert classify(F.relu) == L.ACT_RELU
+    assert classify(torch.nn.GELU(approximate="tanh")) == L.ACT_GELU_TANH
+    assert classify(torch.nn.SiLU()) == L.ACT_SILU
+    assert classify(lambda t: t) == L.ACT_NONE
+    assert classify(lambda t: torch.sigmoid(t)) == -1
+    assert classify(lambda t: t.cuda_only_thing()) == -1
+
+
+def test_checkpoint_buffer_roundtrip_single_rank():
+    from hexa_moe import moe as hmoe
+    m = _toy()
+    buf = hmoe.MoE_Buffer([32, 32], 4, 2, 4, None, True, True)
+    with torch.no_grad():
+        for p in m.parameters():
+            p.normal_()
+    m.save_ckpt(buf)
+    m2 = _toy()
+    m2.load_ckpt(buf)
+    for i in range(2):
+        assert torch.equal(m2.batched_fc1_w[i], m.batched_fc1_w[i]) and torch.equal(m2.batched_fc2_bias[i], m.batched_fc2_bias[i])
+        assert torch.equal(m2.batched_fc1_bias[i], m.batched_fc1_bias[i])

@@ -1,0 +1,126 @@
+"""World-size-2 `gloo` runs of the two multi-device modes on CPU.
+
+The expert math is supplied by the CPU oracle (tests/oracle_backend.py) so that what is tested is
+the host logic around it: hidden-dimension sharding with uneven `mlp_proportion`, the
+pipeline-shared cache's all-gather + unpack, reduce-scatter/average of the expert gradients,
+the model-centric token all-gather and output / input-gradient reduce-scatter."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+import torch.nn.functional as F
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
+
+
+def _full_params(E, d, H, n_layers, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    P = []
+    for _ in range(n_layers):
+        P.append(dict(w1=torch.randn(E, H, d, generator=g) * 0.2, w2=torch.randn(E, H, d, generator=g) * 0.2,
+                      b1=torch.randn(E, H, generator=g) * 0.1, b2=torch.randn(E, d, generator=g) * 0.1,
+                      wg=torch.randn(E, d, generator=g) * 0.5))
+    return P
+
+
+def _worker(rank, world, port, data_centric, proportion, tokens_per_rank, q):
+    sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle_backend
+        from hexa_moe import moe as hmoe
+        from oracle import hexa_oracle as O
+        E, d, H, k, L = 4, 16, 64, 2, 2
+        m = hmoe.MoE_Cascaded(gate_type={'type': 'top', 'k': k, 'fp32_gate': True}, model_dim_list=[d] * L, moe_idx_list=[0, 1],
+                              mlp_ratio=H // d, mlp_proportion=proportion, num_global_experts=E, total_depth=L,
+                              data_centric=data_centric, activation_fn=lambda t: F.gelu(t))
+        m.dispatch_params.backend = oracle_backend          # test double: CPU oracle instead of the CUDA kernels
+        m.eval()
+        P = _full_params(E, d, H, L)
+        split = [m.local_dim_list_all[r][0] for r in range(world)]
+        lo = sum(split[:rank]); n = split[rank]
+        with torch.no_grad():
+            for i in range(L):
+                m.batched_fc1_w[i].zero_(); m.batched_fc2_w[i].zero_(); m.batched_fc1_bias[i].zero_()
+                m.batched_fc1_w[i][:, :n] = P[i]["w1"][:, lo: lo + n]
+                m.batched_fc2_w[i][:, :n] = P[i]["w2"][:, lo: lo + n]
+                m.batched_fc1_bias[i][:, :n] = P[i]["b1"][:, lo: lo + n]
+                m.batched_fc2_bias[i].copy_(P[i]["b2"]); m.gates[i].wg.weight.copy_(P[i]["wg"])
+        xs = [torch.randn(tokens_per_rank[r], d, generator=torch.Generator().manual_seed(100 + r)) for r in range(world)]
+        x = xs[rank].clone().requires_grad_(True)
+        h, aux = x, 0
+        for i in range(L):
+            h, l = m(i, h)
+            aux = aux + l
+        h.sum().backward()
+
+        # expectation from the oracle, layer by layer on every rank's tokens
+        def run_rank(r):
+            cur = xs[r].double().requires_grad_(False)
+            saved = []
+            for i in range(L):
+                ids, _, _ = O.gate_topk(cur.float(), P[i]["wg"], k)
+                res = O.moe_layer(cur, ids, P[i]["w1"], P[i]["w2"], P[i]["b1"], P[i]["b2"], F.gelu)
+                saved.append((cur, ids)); cur = res["y"]
+            y = cur
+            g = torch.ones_like(y); grads = [None] * L
+            for i in reversed(range(L)):
+                cin, ids = saved[i]
+                res = O.moe_layer(cin, ids, P[i]["w1"], P[i]["w2"], P[i]["b1"], P[i]["b2"], F.gelu, g)
+                grads[i] = res; g = res["dx"]
+            return y, g, grads
+        outs = [run_rank(r) for r in range(world)]
+        y_exp, dx_exp, _ = outs[rank]
+        torch.testing.assert_close(h.detach().double(), y_exp, rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(x.grad.double(), dx_exp, rtol=1e-4, atol=1e-4)
+        for i in range(L):
+            if data_centric:   # data parallel over tokens: gradients are averaged over ranks
+                comb = lambda key: sum(outs[r][2][i][key] for r in range(world)) / world
+            else:              # every rank saw all tokens for its hidden slice: plain sum
+                comb = lambda key: sum(outs[r][2][i][key] for r in range(world))
+            torch.testing.assert_close(m.batched_fc1_w[i].grad[:, :n].double(), comb("dw1")[:, lo: lo + n], rtol=1e-4, atol=1e-4)
+            torch.testing.assert_close(m.batched_fc2_w[i].grad[:, :n].double(), comb("dw2")[:, lo: lo + n], rtol=1e-4, atol=1e-4)
+            torch.testing.assert_close(m.batched_fc1_bias[i].grad[:, :n].double(), comb("db1")[:, lo: lo + n], rtol=1e-4, atol=1e-4)
+            torch.testing.assert_close(m.batched_fc2_bias[i].grad.double(), comb("db2"), rtol=1e-4, atol=1e-4)
+            if n < m.batched_fc1_w[i].shape[1]:
+                assert (m.batched_fc1_w[i].grad[:, n:] == 0).all()      # storage padding gets no gradient
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, "FAIL: " + traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(data_centric, proportion, tokens_per_rank):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, data_centric, proportion, tokens_per_rank, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(60)
+    for rank, msg in res:
+        assert msg == "ok", f"rank {rank}: {msg}"
+
+
+@pytest.mark.parametrize("proportion", [None, [0.7, 0.3]])
+def test_data_centric_two_ranks(proportion):
+    _run(True, proportion, [40, 40])
+
+
+@pytest.mark.parametrize("proportion,tokens", [(None, [32, 32]), ([0.3, 0.7], [24, 40])])
+def test_model_centric_two_ranks(proportion, tokens):
+    _run(False, proportion, tokens)
