@@ -8,8 +8,9 @@
 //   warp 0      TMA producer: 128B-swizzled tiles of A and B into a kStages-deep shared-memory ring
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
 //               accumulators, tcgen05.commit releases ring slots and publishes finished accumulators
-//   warps 2..9  epilogue: tcgen05.ld of the accumulator (lane quadrant = warp % 4, two warps per
-//               quadrant split the columns), fused epilogue math, 16-byte global stores
+//   warps 2..   epilogue (16 warps by default): tcgen05.ld of the accumulator (lane quadrant = warp % 4, each
+//               group of four warps owns a column range), fused epilogue math; ESMM results go through a
+//               64B-swizzled staging tile and one TMA store per 128x32 block, ESTMM stores from registers
 // so the epilogue of tile i overlaps the MMAs of tile i+1.  Every mbarrier wait is bounded: after
 // ~2 s a CTA raises an abort flag, records a code in the status word and drains.
 //
@@ -27,8 +28,6 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;   // one 128-byte swizzle span of 16-bit elements
 constexpr int UMMA_K = 16;
-constexpr int kEpiWarps = 8;
-constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr uint32_t kABytes = BLOCK_M * BLOCK_K * 2;  // 16 KB
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
@@ -54,6 +53,8 @@ struct Params {
   int out_f32;      // ESTMM: fp32 output
   int beta;         // ESTMM: accumulate into out
   int mn_swap;      // debug: swap LBO/SBO of MN-major descriptors
+  int prefetch;     // k-blocks an L2 prefetch cursor runs ahead of the TMA loads (0 = off)
+  int direct_store; // ESMM epilogue: 16-byte stores from registers instead of staging + TMA store
   int32_t* status;
 };
 
@@ -182,49 +183,14 @@ __device__ __forceinline__ float unpack_hi(uint32_t w, int is_bf16) {
   return __half2float(__ushort_as_half((unsigned short)(w >> 16)));
 }
 
-// Epilogue of one 32-column chunk of one row: f holds acc + bias.  Writes `ncols` (a multiple of 8) columns.
-//   EPI_ACT    aux (if given) <- f ; c <- act(f)        EPI_DACT   c <- f * act'(aux)        EPI_LINEAR   c <- f
-// Rows that are not live (segment padding) are written as zeros.
-template <int EPI, int ACT>
-__device__ __forceinline__ void store_chunk(const float (&f)[32], uint16_t* cp, uint16_t* xp, int ncols, bool live, int is_bf16) {
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    if (g * 8 >= ncols) break;
-    uint4 w;
-    uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
-    if (EPI == HEXA_EPI_ACT) {
-      if (xp) {
-        uint4 y;
-        uint32_t* yp = reinterpret_cast<uint32_t*>(&y);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) yp[i] = live ? pack2(f[8 * g + 2 * i], f[8 * g + 2 * i + 1], is_bf16) : 0u;
-        *reinterpret_cast<uint4*>(xp + g * 8) = y;
-      }
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        wp[i] = live ? pack2(act_fast<ACT>(f[8 * g + 2 * i]), act_fast<ACT>(f[8 * g + 2 * i + 1]), is_bf16) : 0u;
-    } else if (EPI == HEXA_EPI_DACT) {
-      const uint4 y = *reinterpret_cast<const uint4*>(xp + g * 8);
-      const uint32_t* yp = reinterpret_cast<const uint32_t*>(&y);
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        wp[i] = live ? pack2(f[8 * g + 2 * i] * act_grad_fast<ACT>(unpack_lo(yp[i], is_bf16)),
-                             f[8 * g + 2 * i + 1] * act_grad_fast<ACT>(unpack_hi(yp[i], is_bf16)), is_bf16)
-                     : 0u;
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) wp[i] = live ? pack2(f[8 * g + 2 * i], f[8 * g + 2 * i + 1], is_bf16) : 0u;
-    }
-    *reinterpret_cast<uint4*>(cp + g * 8) = w;
-  }
-}
-
 template <int BN> struct Cfg {
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr uint32_t kBBytes = BN * BLOCK_K * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators; 256 or 512, a power of two
-  static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + 256 /*barriers*/;
+  static constexpr uint32_t kStoreBufBytes = 128 * 64;   // [128 rows x 32 16-bit columns]
+  static constexpr uint32_t kStoreBytes = 4 * kStoreBufBytes;  // shared by the groups of four epilogue warps
+  static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + kStoreBytes + 256 /*barriers*/;
 };
 
 struct Tile {
@@ -262,14 +228,117 @@ __device__ __forceinline__ bool get_tile(const Params& p, int64_t t, Tile& tile)
   }
 }
 
+// Iterator over the (tile, k-block) pairs one CTA processes, skipping tiles without k-blocks.
 template <int BN, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+struct KCursor {
+  int64_t t;
+  Tile tile;
+  int kb;
+  bool valid;
+  __device__ explicit KCursor(const Params& p) : t(blockIdx.x), kb(0) {
+    valid = get_tile<BN, MODE>(p, t, tile);
+    skip_empty(p);
+  }
+  __device__ void skip_empty(const Params& p) {
+    while (valid && tile.num_kb == 0) { t += gridDim.x; valid = get_tile<BN, MODE>(p, t, tile); }
+    kb = 0;
+  }
+  __device__ void next(const Params& p) {
+    if (++kb >= tile.num_kb) { t += gridDim.x; valid = get_tile<BN, MODE>(p, t, tile); skip_empty(p); }
+  }
+};
+
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tm, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(tm), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* tm, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(tm), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// L2 prefetch of exactly the boxes the producer will later load for (tile, kb).
+template <int BN, int MODE>
+__device__ __forceinline__ void prefetch_kblock(const CUtensorMap& tmA, const CUtensorMap& tmB, const Tile& tile, int kb) {
+  if (MODE == ESTMM) {
+    const int r = tile.row0 + kb * BLOCK_K;
+#pragma unroll
+    for (int c = 0; c < BLOCK_M / 64; ++c) tma_prefetch_2d(&tmA, tile.m0 + c * 64, r);
+#pragma unroll
+    for (int c = 0; c < BN / 64; ++c) tma_prefetch_2d(&tmB, tile.col0 + c * 64, r);
+  } else {
+    tma_prefetch_2d(&tmA, kb * BLOCK_K, tile.row0);
+    if (MODE == ESMM_NK) {
+      tma_prefetch_3d(&tmB, kb * BLOCK_K, tile.col0, tile.e);
+    } else {
+#pragma unroll
+      for (int c = 0; c < BN / 64; ++c) tma_prefetch_3d(&tmB, tile.col0 + c * 64, kb * BLOCK_K, tile.e);
+    }
+  }
+}
+
+// ---- epilogue staging: registers -> 64B-swizzled shared memory -> TMA store ------------------------
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tm), "r"(smem_u32(src)),
+               "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// One thread's row (32 columns = 64 B = four 16-byte chunks) into a [128 x 64 B] staging tile laid out
+// as TMA's 64-byte swizzle expects: chunk c of row r lives at chunk c ^ ((r >> 1) & 3).
+__device__ __forceinline__ void stage_row(uint8_t* buf, int r, const uint32_t (&w)[16]) {
+  uint8_t* row = buf + r * 64;
+  const int x = (r >> 1) & 3;
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    *reinterpret_cast<uint4*>(row + ((c ^ x) << 4)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+}
+
+// Values of one row chunk for the two possible outputs of the ESMM epilogue: y = acc + bias packed as it is
+// (the saved pre-activation), o = the layer output of this GEMM.  Rows that are padding produce zeros.
+template <int EPI, int ACT>
+__device__ __forceinline__ void epi_values(const float (&f)[32], const uint16_t* xp, bool live, int ncols, int is_bf16,
+                                           uint32_t (&y)[16], uint32_t (&o)[16]) {
+  if (EPI == HEXA_EPI_DACT) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      // columns at or beyond ncols do not exist (the TMA store clips them): do not read aux there
+      const uint4 a = g * 8 < ncols ? *reinterpret_cast<const uint4*>(xp + g * 8) : make_uint4(0, 0, 0, 0);
+      const uint32_t* ap = reinterpret_cast<const uint32_t*>(&a);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        o[4 * g + i] = live ? pack2(f[8 * g + 2 * i] * act_grad_fast<ACT>(unpack_lo(ap[i], is_bf16)),
+                                    f[8 * g + 2 * i + 1] * act_grad_fast<ACT>(unpack_hi(ap[i], is_bf16)), is_bf16)
+                            : 0u;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (EPI == HEXA_EPI_ACT) {
+        y[i] = live ? pack2(f[2 * i], f[2 * i + 1], is_bf16) : 0u;
+        o[i] = live ? pack2(act_fast<ACT>(f[2 * i]), act_fast<ACT>(f[2 * i + 1]), is_bf16) : 0u;
+      } else {
+        o[i] = live ? pack2(f[2 * i], f[2 * i + 1], is_bf16) : 0u;
+      }
+    }
+  }
+}
+
+template <int BN, int MODE, int EPIW>
+__global__ void __launch_bounds__(32 * (2 + EPIW), 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const Params p) {
   using C = Cfg<BN>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * C::kStageBytes);
+  uint8_t* store_bufs = smem + (size_t)kStages * C::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(store_bufs + C::kStoreBytes);
   uint64_t* full = bars;                  // [kStages]  producer -> MMA
   uint64_t* empty = bars + kStages;       // [kStages]  MMA -> producer
   uint64_t* acc_full = bars + 2 * kStages;        // [2] MMA -> epilogue
@@ -281,7 +350,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], kEpiWarps); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EPIW); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -299,31 +368,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      Tile tile;
-      for (int64_t t = blockIdx.x; ok && get_tile<BN, MODE>(p, t, tile); t += gridDim.x) {
-        for (int kb = 0; kb < tile.num_kb; ++kb) {
-          if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, 1))) break;
-          uint8_t* sA = smem + (size_t)stage * C::kStageBytes;
-          uint8_t* sB = sA + kABytes;
-          mbar_expect_tx(&full[stage], C::kStageBytes);
-          if (MODE == ESTMM) {
-            const int r = tile.row0 + kb * BLOCK_K;
+      // The load cursor walks this CTA's (tile, k-block) sequence; a second cursor can run p.prefetch k-blocks
+      // in front of it and only issues L2 prefetches, so a DRAM miss is paid long before the shared-memory ring
+      // (whose depth covers L2 latency only) needs the data.
+      KCursor<BN, MODE> ld(p), pf(p);
+      for (int i = 0; i < p.prefetch && pf.valid; ++i) { prefetch_kblock<BN, MODE>(tmA, tmB, pf.tile, pf.kb); pf.next(p); }
+      while (ld.valid) {
+        if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, 1))) break;
+        if (p.prefetch > 0 && pf.valid) { prefetch_kblock<BN, MODE>(tmA, tmB, pf.tile, pf.kb); pf.next(p); }
+        const Tile& tile = ld.tile;
+        const int kb = ld.kb;
+        uint8_t* sA = smem + (size_t)stage * C::kStageBytes;
+        uint8_t* sB = sA + kABytes;
+        mbar_expect_tx(&full[stage], C::kStageBytes);
+        if (MODE == ESTMM) {
+          const int r = tile.row0 + kb * BLOCK_K;
 #pragma unroll
-            for (int c = 0; c < BLOCK_M / 64; ++c) tma_load_2d(sA + c * 8192, &tmA, &full[stage], tile.m0 + c * 64, r);
+          for (int c = 0; c < BLOCK_M / 64; ++c) tma_load_2d(sA + c * 8192, &tmA, &full[stage], tile.m0 + c * 64, r);
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sB + c * 8192, &tmB, &full[stage], tile.col0 + c * 64, r);
+          for (int c = 0; c < BN / 64; ++c) tma_load_2d(sB + c * 8192, &tmB, &full[stage], tile.col0 + c * 64, r);
+        } else {
+          tma_load_2d(sA, &tmA, &full[stage], kb * BLOCK_K, tile.row0);
+          if (MODE == ESMM_NK) {
+            tma_load_3d(sB, &tmB, &full[stage], kb * BLOCK_K, tile.col0, tile.e);
           } else {
-            tma_load_2d(sA, &tmA, &full[stage], kb * BLOCK_K, tile.row0);
-            if (MODE == ESMM_NK) {
-              tma_load_3d(sB, &tmB, &full[stage], kb * BLOCK_K, tile.col0, tile.e);
-            } else {
 #pragma unroll
-              for (int c = 0; c < BN / 64; ++c)
-                tma_load_3d(sB + c * 8192, &tmB, &full[stage], tile.col0 + c * 64, kb * BLOCK_K, tile.e);
-            }
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_3d(sB + c * 8192, &tmB, &full[stage], tile.col0 + c * 64, kb * BLOCK_K, tile.e);
           }
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        ld.next(p);
       }
     }
     __syncwarp();
@@ -375,9 +450,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue
+    constexpr int kParts = EPIW / 4;        // groups of four warps; each group owns BN / kParts columns of every tile
+    constexpr int kBufsPerPart = 4 / kParts;
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;       // which half of the BN columns
+    const int part = (warp - 2) >> 2;
     const int is_bf16 = p.is_bf16;
+    const bool leader = (q == 2) && lane == 0;   // the first warp of every group of four issues the group's TMA stores
+    uint32_t store_seq = 0;
     bool ok = true;
     Tile tile;
     int it = 0;
@@ -389,8 +468,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int rloc = q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
-      for (int cc = 0; cc < BN / 2 / 32; ++cc) {
-        const int cloc = half * (BN / 2) + cc * 32;
+      for (int cc = 0; cc < BN / kParts / 32; ++cc) {
+        const int cloc = part * (BN / kParts) + cc * 32;
         const int64_t gcol = (int64_t)tile.col0 + cloc;
         if (gcol >= p.n) break;  // uniform across the warp
         uint32_t v[32];
@@ -457,20 +536,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               }
             }
           }
-          uint16_t* cp = reinterpret_cast<uint16_t*>(p.c) + r * p.ldc + gcol;
-          uint16_t* xp = p.aux ? reinterpret_cast<uint16_t*>(p.aux) + r * p.ldaux + gcol : nullptr;
+          const uint16_t* xp = p.aux ? reinterpret_cast<const uint16_t*>(p.aux) + r * p.ldaux + gcol : nullptr;
+          uint32_t yv[16], ov[16];
           const int ncols = (int)min((int64_t)32, p.n - gcol);
           switch (p.epilogue * 8 + p.act) {
-            case HEXA_EPI_ACT * 8 + HEXA_ACT_RELU: store_chunk<HEXA_EPI_ACT, HEXA_ACT_RELU>(f, cp, xp, ncols, live, is_bf16); break;
-            case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU: store_chunk<HEXA_EPI_ACT, HEXA_ACT_GELU>(f, cp, xp, ncols, live, is_bf16); break;
-            case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU_TANH: store_chunk<HEXA_EPI_ACT, HEXA_ACT_GELU_TANH>(f, cp, xp, ncols, live, is_bf16); break;
-            case HEXA_EPI_ACT * 8 + HEXA_ACT_SILU: store_chunk<HEXA_EPI_ACT, HEXA_ACT_SILU>(f, cp, xp, ncols, live, is_bf16); break;
-            case HEXA_EPI_ACT * 8 + HEXA_ACT_NONE: store_chunk<HEXA_EPI_ACT, HEXA_ACT_NONE>(f, cp, xp, ncols, live, is_bf16); break;
-            case HEXA_EPI_DACT * 8 + HEXA_ACT_RELU: store_chunk<HEXA_EPI_DACT, HEXA_ACT_RELU>(f, cp, xp, ncols, live, is_bf16); break;
-            case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU: store_chunk<HEXA_EPI_DACT, HEXA_ACT_GELU>(f, cp, xp, ncols, live, is_bf16); break;
-            case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU_TANH: store_chunk<HEXA_EPI_DACT, HEXA_ACT_GELU_TANH>(f, cp, xp, ncols, live, is_bf16); break;
-            case HEXA_EPI_DACT * 8 + HEXA_ACT_SILU: store_chunk<HEXA_EPI_DACT, HEXA_ACT_SILU>(f, cp, xp, ncols, live, is_bf16); break;
-            default: store_chunk<HEXA_EPI_LINEAR, HEXA_ACT_NONE>(f, cp, xp, ncols, live, is_bf16); break;
+            case HEXA_EPI_ACT * 8 + HEXA_ACT_RELU: epi_values<HEXA_EPI_ACT, HEXA_ACT_RELU>(f, xp, live, ncols, is_bf16, yv, ov); break;
+            case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU: epi_values<HEXA_EPI_ACT, HEXA_ACT_GELU>(f, xp, live, ncols, is_bf16, yv, ov); break;
+            case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU_TANH: epi_values<HEXA_EPI_ACT, HEXA_ACT_GELU_TANH>(f, xp, live, ncols, is_bf16, yv, ov); break;
+            case HEXA_EPI_ACT * 8 + HEXA_ACT_SILU: epi_values<HEXA_EPI_ACT, HEXA_ACT_SILU>(f, xp, live, ncols, is_bf16, yv, ov); break;
+            case HEXA_EPI_ACT * 8 + HEXA_ACT_NONE: epi_values<HEXA_EPI_ACT, HEXA_ACT_NONE>(f, xp, live, ncols, is_bf16, yv, ov); break;
+            case HEXA_EPI_DACT * 8 + HEXA_ACT_RELU: epi_values<HEXA_EPI_DACT, HEXA_ACT_RELU>(f, xp, live, ncols, is_bf16, yv, ov); break;
+            case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU: epi_values<HEXA_EPI_DACT, HEXA_ACT_GELU>(f, xp, live, ncols, is_bf16, yv, ov); break;
+            case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU_TANH: epi_values<HEXA_EPI_DACT, HEXA_ACT_GELU_TANH>(f, xp, live, ncols, is_bf16, yv, ov); break;
+            case HEXA_EPI_DACT * 8 + HEXA_ACT_SILU: epi_values<HEXA_EPI_DACT, HEXA_ACT_SILU>(f, xp, live, ncols, is_bf16, yv, ov); break;
+            default: epi_values<HEXA_EPI_LINEAR, HEXA_ACT_NONE>(f, xp, live, ncols, is_bf16, yv, ov); break;
+          }
+          // registers -> swizzled staging tile -> one TMA store per 128x32 block (full 128-byte lines to L2);
+          // a group with two buffers alternates them, so at most one earlier store may still be reading
+          const bool two = (p.epilogue == HEXA_EPI_ACT) && p.aux != nullptr;
+          for (int o = two ? 0 : 1; o < 2; ++o) {
+            if (p.direct_store) {
+              uint16_t* dst = reinterpret_cast<uint16_t*>(o == 0 ? p.aux : p.c) + r * (o == 0 ? p.ldaux : p.ldc) + gcol;
+              const uint32_t* w = o == 0 ? yv : ov;
+#pragma unroll
+              for (int g = 0; g < 4; ++g)
+                if (g * 8 < ncols) *reinterpret_cast<uint4*>(dst + g * 8) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+              continue;
+            }
+            uint8_t* buf = store_bufs + (size_t)(part * kBufsPerPart + (store_seq % kBufsPerPart)) * C::kStoreBufBytes;
+            ++store_seq;
+            if (leader) bulk_wait_read<kBufsPerPart - 1>();
+            group_sync(1 + part);
+            stage_row(buf, rloc, o == 0 ? yv : ov);
+            fence_async_smem();
+            group_sync(1 + part);
+            if (leader) {
+              tma_store_2d(o == 0 ? &tmX : &tmC, buf, (int)gcol, tile.row0);
+              bulk_commit();
+            }
           }
         }
       }
@@ -479,6 +582,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
     }
+    if (leader) bulk_wait_all();   // staging buffers must outlive the stores that read them
   }
 
   // ------------------------------------------------------------------ teardown
@@ -508,16 +612,16 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-// rank-2 or rank-3 map over 16-bit elements, 128-byte swizzle, zero fill out of bounds
+// rank-2 or rank-3 map over 16-bit elements, 128-byte swizzle unless told otherwise, zero fill out of bounds
 int make_map(CUtensorMap* tm, const void* base, int is_bf16, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-             const uint32_t* box) {
+             const uint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   auto fn = encode_fn();
   if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return HEXA_ERR_CUDA; }
   cuuint64_t d[3]; cuuint64_t s[2]; cuuint32_t b[3]; cuuint32_t es[3] = {1, 1, 1};
   for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; }
   for (int i = 0; i + 1 < rank; ++i) s[i] = strides_bytes[i];
   CUresult r = fn(tm, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank,
-                  const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed with CUresult %d (rank %d dims %llu,%llu box %u,%u)", (int)r, rank,
@@ -527,21 +631,42 @@ int make_map(CUtensorMap* tm, const void* base, int is_bf16, int rank, const uin
   return HEXA_OK;
 }
 
-template <int BN, int MODE>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, int64_t max_tiles, cudaStream_t stream) {
+template <int BN, int MODE, int EPIW>
+int launch_w(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX, const Params& p,
+             int64_t max_tiles, cudaStream_t stream) {
   using C = Cfg<BN>;
   static bool attr_set[64] = {false};
   int dev = 0;
   HEXA_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    HEXA_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
+    HEXA_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, EPIW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
     attr_set[dev] = true;
   }
   int64_t grid = max_tiles < sm_count() ? max_tiles : sm_count();
   if (grid <= 0) return HEXA_OK;
-  gemm_tc_kernel<BN, MODE><<<(unsigned)grid, kThreads, C::kSmemBytes, stream>>>(tmA, tmB, p);
+  gemm_tc_kernel<BN, MODE, EPIW><<<(unsigned)grid, 32 * (2 + EPIW), C::kSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
   HEXA_LAUNCH_CHECK("gemm_tc_kernel");
   return HEXA_OK;
+}
+
+int env_int(const char* name, int dflt) {
+  const char* s = getenv(name);
+  return s ? atoi(s) : dflt;
+}
+int epi_warps() { static int v = -1; if (v < 0) v = env_int("HEXA_EPI_WARPS", 16) == 8 ? 8 : 16; return v; }
+int direct_store_flag() { static int v = -1; if (v < 0) v = env_int("HEXA_DIRECT_STORE", 0) ? 1 : 0; return v; }
+
+template <int BN, int MODE>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX, const Params& p,
+           int64_t max_tiles, cudaStream_t stream) {
+  if (epi_warps() == 16) return launch_w<BN, MODE, 16>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
+  return launch_w<BN, MODE, 8>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
+}
+
+int prefetch_depth() {
+  static int v = -1;
+  if (v < 0) { const char* s = getenv("HEXA_L2_PREFETCH"); v = s ? atoi(s) : 0; if (v < 0 || v > 64) v = 0; }
+  return v;
 }
 
 int mn_swap_flag() {
@@ -589,15 +714,32 @@ int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int6
     int rc = make_map(&tmB, b, is_bf16, 3, dims, str, box);
     if (rc) return rc;
   }
+  // output maps for the epilogue's TMA stores: [128 rows x 32 columns] boxes, 64-byte swizzle
+  CUtensorMap tmC, tmX;
+  {
+    uint64_t dims[2] = {(uint64_t)n_out, (uint64_t)row_cap};
+    uint32_t box[2] = {32, BLOCK_M};
+    uint64_t str[1] = {(uint64_t)ldc * 2};
+    int rc = make_map(&tmC, c, is_bf16, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+    tmX = tmC;
+    if (aux && epilogue == HEXA_EPI_ACT) {
+      uint64_t strx[1] = {(uint64_t)ldaux * 2};
+      rc = make_map(&tmX, aux, is_bf16, 2, dims, strx, box, CU_TENSOR_MAP_SWIZZLE_64B);
+      if (rc) return rc;
+    }
+  }
   Params p{};
   p.tile_expert = tile_expert; p.pad_offsets = pad_offsets; p.row_token = row_token;
   p.bias = bias; p.ldbias = ldbias; p.aux = aux; p.ldaux = ldaux; p.c = c; p.ldc = ldc;
   p.n = n_out; p.k = k; p.m = 0; p.E = E; p.epilogue = epilogue; p.act = act; p.is_bf16 = is_bf16;
-  p.mn_swap = mn_swap_flag(); p.status = status_word();
+  p.mn_swap = mn_swap_flag(); p.prefetch = prefetch_depth(); p.direct_store = direct_store_flag(); p.status = status_word();
   const int64_t max_tiles = (row_cap / BLOCK_M) * ceil_div(n_out, BN);
   if (b_layout == HEXA_B_NK)
-    return BN == 256 ? launch<256, ESMM_NK>(tmA, tmB, p, max_tiles, stream) : launch<128, ESMM_NK>(tmA, tmB, p, max_tiles, stream);
-  return BN == 256 ? launch<256, ESMM_KN>(tmA, tmB, p, max_tiles, stream) : launch<128, ESMM_KN>(tmA, tmB, p, max_tiles, stream);
+    return BN == 256 ? launch<256, ESMM_NK>(tmA, tmB, tmC, tmX, p, max_tiles, stream)
+                     : launch<128, ESMM_NK>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
+  return BN == 256 ? launch<256, ESMM_KN>(tmA, tmB, tmC, tmX, p, max_tiles, stream)
+                   : launch<128, ESMM_KN>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
 }
 
 bool estmm_tc_supported(const void* p, int64_t ldp, const void* q, int64_t ldq, const void* out, int64_t ldo,
@@ -635,9 +777,11 @@ int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, con
   Params p{};
   p.pad_offsets = pad_offsets; p.c = out; p.ldc = ldo; p.c_estride = o_estride; p.n = n; p.m = m; p.E = E;
   p.is_bf16 = is_bf16; p.out_f32 = out_dtype == HEXA_F32; p.beta = beta; p.mn_swap = mn_swap_flag();
-  p.status = status_word();
+  p.prefetch = prefetch_depth(); p.status = status_word();
   const int64_t max_tiles = (int64_t)E * ceil_div(m, BLOCK_M) * ceil_div(n, BN);
-  return BN == 256 ? launch<256, ESTMM>(tmA, tmB, p, max_tiles, stream) : launch<128, ESTMM>(tmA, tmB, p, max_tiles, stream);
+  // ESTMM stores straight from registers; the two output maps are unused placeholders
+  return BN == 256 ? launch<256, ESTMM>(tmA, tmB, tmA, tmA, p, max_tiles, stream)
+                   : launch<128, ESTMM>(tmA, tmB, tmA, tmA, p, max_tiles, stream);
 }
 
 }  // namespace hexa
