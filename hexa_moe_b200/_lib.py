@@ -40,6 +40,8 @@ SIGNATURES = {
     "hexa_ess_workspace_bytes": (sz, [i64, i64]),
     "hexa_ess": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, ci, vp, sz, vp]),
     "hexa_mask_pad_rows": (ci, [vp, i64, vp, vp, ci, i64, i64, ci, vp]),
+    "hexa_ess_static_capacity_bytes": (sz, []),
+    "hexa_ess_static": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, ci, vp]),
 }
 
 _lock = threading.Lock()

@@ -257,3 +257,41 @@ extern "C" int hexa_ess(const void* src, int64_t src_ld, const int32_t* pad_offs
   }
   return ess_launch(src, src_ld, pad_offsets, E, row_cap, cols, out, ldo, dtype, (float*)workspace, (cudaStream_t)stream_);
 }
+
+// ---- ESS on library-owned scratch -------------------------------------------------------------------
+// Pass 1 of ESS needs one fp32 partial row per 128 sorted rows.  hexa_ess takes that scratch from the
+// caller; this variant keeps it in a fixed array inside the library instead, for callers that have no
+// way to obtain device memory at the point of the call.
+namespace hexa {
+constexpr size_t kEssStaticFloats = (size_t)8 << 20;   // 8 Mi floats = 32 MiB, resident on every device that loads the library
+static __device__ __align__(256) float g_ess_static_scratch[kEssStaticFloats];
+}  // namespace hexa
+
+extern "C" size_t hexa_ess_static_capacity_bytes(void) { return hexa::kEssStaticFloats * sizeof(float); }
+
+extern "C" int hexa_ess_static(const void* src, int64_t src_ld, const int32_t* pad_offsets, int E, int64_t row_cap,
+                               int64_t cols, float* out, int64_t ldo, int dtype, void* stream_) {
+  HEXA_REQUIRE(src && pad_offsets && out, "hexa_ess_static: null pointer");
+  HEXA_REQUIRE(E > 0 && E <= 65535 && row_cap >= 0 && cols > 0 && src_ld >= cols && ldo >= cols, "hexa_ess_static: bad sizes");
+  HEXA_REQUIRE(aligned16(src), "hexa_ess_static: src must be 16-byte aligned");
+  const size_t need = hexa_ess_workspace_bytes(row_cap, cols);
+  if (need > kEssStaticFloats * sizeof(float)) {
+    set_error("hexa_ess_static: needs %zu bytes of scratch (row_capacity/128 * cols floats) but the built-in buffer holds %zu; "
+              "use hexa_ess with caller-provided workspace for this size",
+              need, kEssStaticFloats * sizeof(float));
+    return HEXA_ERR_WORKSPACE;
+  }
+  // The array's name is only a host-side handle; the kernels need its address on the current device.
+  // Looked up once per device, with that device current (first call on a device: do it before any stream capture).
+  static float* dev_addr[64] = {nullptr};
+  int dev = 0;
+  HEXA_CUDA(cudaGetDevice(&dev));
+  HEXA_REQUIRE(dev >= 0 && dev < 64, "hexa_ess_static: device ordinal %d out of range", dev);
+  float* scratch = __atomic_load_n(&dev_addr[dev], __ATOMIC_ACQUIRE);
+  if (!scratch) {
+    HEXA_CUDA(cudaGetSymbolAddress((void**)&scratch, g_ess_static_scratch));
+    __atomic_store_n(&dev_addr[dev], scratch, __ATOMIC_RELEASE);
+  }
+  // Nothing in the scratch has to start at zero: pass 1 overwrites every partial row that pass 2 reads.
+  return ess_launch(src, src_ld, pad_offsets, E, row_cap, cols, out, ldo, dtype, scratch, (cudaStream_t)stream_);
+}

@@ -144,6 +144,24 @@ int hexa_ess(const void* src, int64_t src_ld, const int32_t* pad_offsets, int nu
              int64_t row_capacity, int64_t cols, float* out, int64_t ldo, int dtype, void* workspace,
              size_t workspace_bytes, void* stream);
 
+/* ESS without caller-provided scratch.  No counterpart in the reference (its launchers cudaMalloc their
+ * own scratch on every call, kernels/shared_cuda_core.cu:304-309).  Same result as hexa_ess, bit for bit,
+ * but pass 1's partial sums live in a fixed 32 MiB array inside the library, so the call allocates nothing
+ * and needs no workspace argument.  It is meant for callers that cannot get device memory where the call
+ * is made: code running inside an allocator-free region (a custom autograd node or a framework callback
+ * that must not touch the caching allocator), or a plain-C host that holds only the input and output
+ * pointers it was handed.  Limits and caveats:
+ *   - ceil(row_capacity/128) * cols * 4 bytes must fit in hexa_ess_static_capacity_bytes(); larger requests
+ *     fail with HEXA_ERR_WORKSPACE and a message naming both sizes (use hexa_ess then);
+ *   - every GPU that loads the library holds the 32 MiB until the process exits;
+ *   - all calls on a device share the one array: two calls that may overlap on the GPU (different streams)
+ *     race - serialise them; contents from the previous call are left behind and never read;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call outside any stream capture. */
+size_t hexa_ess_static_capacity_bytes(void);
+int hexa_ess_static(const void* src, int64_t src_ld, const int32_t* pad_offsets, int num_experts,
+                    int64_t row_capacity, int64_t cols, float* out, int64_t ldo, int dtype, void* stream);
+
 /* Elementwise helper on sorted rows for activations the epilogue does not know:
  * dst[r,:] = row_token[r] >= 0 ? src[r,:] : 0 (restores the zero-pad-row invariant). */
 int hexa_mask_pad_rows(void* buf, int64_t ld, const int32_t* row_token, const int32_t* pad_offsets,
