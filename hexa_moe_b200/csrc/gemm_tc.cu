@@ -4,18 +4,29 @@
 //   ESTMM  out[e]  = p_e^T x q_e             (contraction over the expert's ragged row segment; both
 //                    operands are MN-major in shared memory, no transposed copy is ever made)
 //
-// One persistent CTA per SM walks a static tile list (tile = blockIdx.x + i*gridDim.x).  Warp roles:
-//   warp 0      TMA producer: 128B-swizzled tiles of A and B into a kStages-deep shared-memory ring
-//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
-//               accumulators, tcgen05.commit releases ring slots and publishes finished accumulators
-//   warps 2..   epilogue (16 warps by default): tcgen05.ld of the accumulator (lane quadrant = warp % 4, each
-//               group of four warps owns a column range), fused epilogue math; ESMM results go through a
-//               64B-swizzled staging tile and one TMA store per 128x32 block, ESTMM stores from registers
-// so the epilogue of tile i overlaps the MMAs of tile i+1.  Every mbarrier wait is bounded: after
-// ~2 s a CTA raises an abort flag, records a code in the status word and drains.
+// Persistent kernel, static tile list.  Two flavours of the same code (template parameter CTAS):
+//   CTAS = 1  one CTA per SM computes a 128 x BN tile (tcgen05 cta_group::1)
+//   CTAS = 2  a cluster of two CTAs on neighbouring SMs computes a 256 x 256 tile (cta_group::2): each CTA
+//             loads its own 128 rows of A and only HALF of the B tile, the pair's MMA reads both halves, and
+//             each CTA keeps its 128 x 256 accumulator in its own TMEM.  Shared-memory fill traffic per MMA
+//             drops from 48 KB to 32 KB per SM per 64-deep k-block, which is what bounds the 1-CTA kernel.
+//             No TMA multicast is used.
+// Warp roles in every CTA:
+//   warp 0      TMA producer: 128B-swizzled k-blocks of A and B into a ring of shared-memory stages
+//   warp 1      MMA issuer (only in the pair's leader CTA when CTAS = 2): one thread issues tcgen05.mma
+//               (K = 16 per instruction) into one of two TMEM accumulators; tcgen05.commit frees ring slots
+//               and publishes finished accumulators (multicast to both CTAs of a pair)
+//   warps 2..   epilogue (16 warps): tcgen05.ld of the accumulator (lane quadrant = warp % 4, each group of
+//               four warps owns a column range), fused epilogue math; ESMM results go through a 64B-swizzled
+//               staging tile and one TMA store per 128x32 block, ESTMM stores from registers
+// so the epilogue of tile i overlaps the MMAs of tile i+1.  Every mbarrier wait is bounded: after ~2 s a CTA
+// raises an abort flag, records a code in the status word and drains; both CTAs of a pair always reach the
+// closing cluster barrier.
 //
-// Segments are aligned to 128 rows, so an ESMM tile never straddles two experts and an ESTMM
-// k-block (64 rows) never reads another expert's rows; pad rows hold zeros and add nothing.
+// Segments are aligned to 128 rows, so an ESMM row block never straddles two experts and an ESTMM k-block
+// (64 rows) never reads another expert's rows; pad rows hold zeros and add nothing.  A pair tile takes two
+// consecutive row blocks of the same expert (list built by the routing step); an expert with an odd number of
+// blocks leaves the second CTA of its last pair without rows to store.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <stdlib.h>
@@ -28,6 +39,8 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;   // one 128-byte swizzle span of 16-bit elements
 constexpr int UMMA_K = 16;
+constexpr int kEpiWarps = 16;
+constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr uint32_t kABytes = BLOCK_M * BLOCK_K * 2;  // 16 KB
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
@@ -37,6 +50,8 @@ struct Params {
   const int32_t* tile_expert;
   const int32_t* pad_offsets;
   const int32_t* row_token;
+  const int32_t* pair_block;   // CTAS = 2, ESMM: per pair tile (first 128-row block) * 2 + (second block belongs to the same expert), -1 ends the list
+  int64_t max_pairs;
   const float* bias;
   int64_t ldbias;
   void* aux;
@@ -52,9 +67,7 @@ struct Params {
   int is_bf16;      // 16-bit flavour of the inputs (and of 16-bit outputs)
   int out_f32;      // ESTMM: fp32 output
   int beta;         // ESTMM: accumulate into out
-  int mn_swap;      // debug: swap LBO/SBO of MN-major descriptors
-  int prefetch;     // k-blocks an L2 prefetch cursor runs ahead of the TMA loads (0 = off)
-  int direct_store; // ESMM epilogue: 16-byte stores from registers instead of staging + TMA store
+  int debug;        // measurement aid (HEXA_TC_DEBUG): bit 0 = producer skips the TMA loads, bit 1 = MMA thread skips the MMAs
   int32_t* status;
 };
 
@@ -83,6 +96,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait that lets the hardware park the thread for up to ~`hint_ns` before it reports "not yet"
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -93,8 +118,8 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int code) {
   uint32_t spins = 0;
   uint64_t t0 = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0xFF) == 0) {
+  while (!mbar_try_wait_hint(bar, parity, 4000u)) {
+    if ((++spins & 0x3F) == 0) {
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) {
@@ -107,6 +132,12 @@ __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile 
     }
   }
   return true;
+}
+
+// Fast path of a bounded wait: one try_wait inline, the timed loop only when the barrier is not ready yet.
+__device__ __forceinline__ bool mbar_wait_fast(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait(bar, parity, abort_flag, status, code);
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, uint64_t* bar, int c0, int c1) {
@@ -183,95 +214,117 @@ __device__ __forceinline__ float unpack_hi(uint32_t w, int is_bf16) {
   return __half2float(__ushort_as_half((unsigned short)(w >> 16)));
 }
 
-template <int BN> struct Cfg {
-  static constexpr int kStages = BN == 256 ? 4 : 6;
-  static constexpr uint32_t kBBytes = BN * BLOCK_K * 2;
+
+// ---- cluster / cta_group::2 helpers -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA loads of a CTA pair: data lands in the issuing CTA's shared memory, the byte count is credited to the
+// mbarrier at `bar_cluster_addr` (the leader CTA's).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* tm, uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(tm), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* tm, uint32_t bar_cluster_addr, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(tm), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"(mask)
+               : "memory");
+}
+
+template <int BN, int CTAS> struct Cfg {
+  static constexpr int kStages = (BN == 256 && CTAS == 1) ? 4 : 6;
+  static constexpr uint32_t kBBytes = (BN / CTAS) * BLOCK_K * 2;   // this CTA's share of the B tile
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators; 256 or 512, a power of two
   static constexpr uint32_t kStoreBufBytes = 128 * 64;   // [128 rows x 32 16-bit columns]
-  static constexpr uint32_t kStoreBytes = 4 * kStoreBufBytes;  // shared by the groups of four epilogue warps
+  static constexpr uint32_t kStoreBytes = 4 * kStoreBufBytes;  // one buffer per group of four epilogue warps
   static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + kStoreBytes + 256 /*barriers*/;
 };
 
 struct Tile {
   int e;          // expert
-  int row0;       // ESMM: first sorted row of the tile ; ESTMM: first row of the expert's segment
-  int col0;       // first output column
-  int m0;         // ESTMM: first output row
+  int row0;       // ESMM: first sorted row of this CTA's block ; ESTMM: first row of the expert's segment
+  int col0;       // first output column of the tile
+  int m0;         // ESTMM: first output row of this CTA's block
   int num_kb;     // k-blocks to accumulate
+  int valid;      // this CTA has rows to store (the second CTA of a pair may not)
 };
 
-template <int BN, int MODE>
-__device__ __forceinline__ bool get_tile(const Params& p, int64_t t, Tile& tile) {
+// Tile t of the static list, as seen by CTA `rank` of its pair (rank = 0 when CTAS = 1).  Returns false past the end.
+template <int BN, int MODE, int CTAS>
+__device__ __forceinline__ bool get_tile(const Params& p, int64_t t, int rank, Tile& tile) {
   if (MODE == ESTMM) {
-    const int64_t MT = (p.m + BLOCK_M - 1) / BLOCK_M, NT = (p.n + BN - 1) / BN;
+    const int64_t MT = (p.m + BLOCK_M * CTAS - 1) / (BLOCK_M * CTAS), NT = (p.n + BN - 1) / BN;
     if (t >= (int64_t)p.E * MT * NT) return false;
     const int e = (int)(t / (MT * NT));
     const int64_t rem = t - (int64_t)e * MT * NT;
     tile.e = e;
-    tile.m0 = (int)(rem / NT) * BLOCK_M;
+    tile.m0 = ((int)(rem / NT) * CTAS + rank) * BLOCK_M;
     tile.col0 = (int)(rem % NT) * BN;
     tile.row0 = p.pad_offsets[e];
     tile.num_kb = (p.pad_offsets[e + 1] - tile.row0) / BLOCK_K;
+    tile.valid = tile.m0 < p.m;
     return true;
   } else {
     const int64_t NT = (p.n + BN - 1) / BN;
-    const int64_t mblocks = p.pad_offsets[p.E] / BLOCK_M;
-    if (t >= mblocks * NT) return false;
-    const int64_t mb = t / NT;
-    tile.e = p.tile_expert[mb];
+    int64_t mb;
+    if (CTAS == 2) {
+      const int64_t pr = t / NT;
+      if (pr >= p.max_pairs) return false;
+      const int pb = p.pair_block[pr];
+      if (pb < 0) return false;
+      mb = (pb >> 1);
+      tile.e = p.tile_expert[mb];
+      tile.valid = rank == 0 || (pb & 1);
+      mb += rank;
+    } else {
+      const int64_t mblocks = p.pad_offsets[p.E] / BLOCK_M;
+      if (t >= mblocks * NT) return false;
+      mb = t / NT;
+      tile.e = p.tile_expert[mb];
+      tile.valid = 1;
+    }
     tile.row0 = (int)(mb * BLOCK_M);
     tile.col0 = (int)(t % NT) * BN;
     tile.m0 = 0;
     tile.num_kb = (int)((p.k + BLOCK_K - 1) / BLOCK_K);
     return tile.e >= 0;
-  }
-}
-
-// Iterator over the (tile, k-block) pairs one CTA processes, skipping tiles without k-blocks.
-template <int BN, int MODE>
-struct KCursor {
-  int64_t t;
-  Tile tile;
-  int kb;
-  bool valid;
-  __device__ explicit KCursor(const Params& p) : t(blockIdx.x), kb(0) {
-    valid = get_tile<BN, MODE>(p, t, tile);
-    skip_empty(p);
-  }
-  __device__ void skip_empty(const Params& p) {
-    while (valid && tile.num_kb == 0) { t += gridDim.x; valid = get_tile<BN, MODE>(p, t, tile); }
-    kb = 0;
-  }
-  __device__ void next(const Params& p) {
-    if (++kb >= tile.num_kb) { t += gridDim.x; valid = get_tile<BN, MODE>(p, t, tile); skip_empty(p); }
-  }
-};
-
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tm, int c0, int c1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(tm), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* tm, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(tm), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-
-// L2 prefetch of exactly the boxes the producer will later load for (tile, kb).
-template <int BN, int MODE>
-__device__ __forceinline__ void prefetch_kblock(const CUtensorMap& tmA, const CUtensorMap& tmB, const Tile& tile, int kb) {
-  if (MODE == ESTMM) {
-    const int r = tile.row0 + kb * BLOCK_K;
-#pragma unroll
-    for (int c = 0; c < BLOCK_M / 64; ++c) tma_prefetch_2d(&tmA, tile.m0 + c * 64, r);
-#pragma unroll
-    for (int c = 0; c < BN / 64; ++c) tma_prefetch_2d(&tmB, tile.col0 + c * 64, r);
-  } else {
-    tma_prefetch_2d(&tmA, kb * BLOCK_K, tile.row0);
-    if (MODE == ESMM_NK) {
-      tma_prefetch_3d(&tmB, kb * BLOCK_K, tile.col0, tile.e);
-    } else {
-#pragma unroll
-      for (int c = 0; c < BN / 64; ++c) tma_prefetch_3d(&tmB, tile.col0 + c * 64, kb * BLOCK_K, tile.e);
-    }
   }
 }
 
@@ -329,138 +382,178 @@ __device__ __forceinline__ void epi_values(const float (&f)[32], const uint16_t*
   }
 }
 
-template <int BN, int MODE, int EPIW>
-__global__ void __launch_bounds__(32 * (2 + EPIW), 1)
+template <int BN, int MODE, int CTAS>
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const Params p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CTAS>;
   constexpr int kStages = C::kStages;
+  constexpr int BNH = BN / CTAS;          // B columns this CTA loads
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* store_bufs = smem + (size_t)kStages * C::kStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(store_bufs + C::kStoreBytes);
-  uint64_t* full = bars;                  // [kStages]  producer -> MMA
-  uint64_t* empty = bars + kStages;       // [kStages]  MMA -> producer
-  uint64_t* acc_full = bars + 2 * kStages;        // [2] MMA -> epilogue
-  uint64_t* acc_empty = bars + 2 * kStages + 2;   // [2] epilogue -> MMA
+  uint64_t* full = bars;                  // [kStages]  producers -> MMA     (used in the leader CTA)
+  uint64_t* empty = bars + kStages;       // [kStages]  MMA -> producer      (one per CTA, multicast commit)
+  uint64_t* acc_full = bars + 2 * kStages;        // [2] MMA -> epilogue     (one per CTA, multicast commit)
+  uint64_t* acc_empty = bars + 2 * kStages + 2;   // [2] epilogues -> MMA    (used in the leader CTA)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = CTAS == 2 ? (int)cluster_ctarank() : 0;    // 0 = leader of the pair
+  const int64_t tile_first = CTAS == 2 ? (blockIdx.x >> 1) : blockIdx.x;
+  const int64_t tile_step = CTAS == 2 ? (gridDim.x >> 1) : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EPIW); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], kEpiWarps * CTAS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {  // the allocating warp also frees
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::kTmemCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (warp == 1) {  // the allocating warp also frees; with CTAS = 2 the same warp of both CTAs takes part
+    if (CTAS == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();   // the peer's barriers exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer (every CTA)
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      // The load cursor walks this CTA's (tile, k-block) sequence; a second cursor can run p.prefetch k-blocks
-      // in front of it and only issues L2 prefetches, so a DRAM miss is paid long before the shared-memory ring
-      // (whose depth covers L2 latency only) needs the data.
-      KCursor<BN, MODE> ld(p), pf(p);
-      for (int i = 0; i < p.prefetch && pf.valid; ++i) { prefetch_kblock<BN, MODE>(tmA, tmB, pf.tile, pf.kb); pf.next(p); }
-      while (ld.valid) {
-        if (!(ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, 1))) break;
-        if (p.prefetch > 0 && pf.valid) { prefetch_kblock<BN, MODE>(tmA, tmB, pf.tile, pf.kb); pf.next(p); }
-        const Tile& tile = ld.tile;
-        const int kb = ld.kb;
-        uint8_t* sA = smem + (size_t)stage * C::kStageBytes;
-        uint8_t* sB = sA + kABytes;
-        mbar_expect_tx(&full[stage], C::kStageBytes);
-        if (MODE == ESTMM) {
-          const int r = tile.row0 + kb * BLOCK_K;
+      Tile tile;
+      const uint32_t lead_full0 = CTAS == 2 ? map_to_cta(&full[0], 0) : 0u;   // the leader CTA's first full barrier
+      for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step) {
+        for (int kb = 0; kb < tile.num_kb; ++kb) {
+          if (!(ok = mbar_wait_fast(&empty[stage], phase ^ 1, abort_flag, p.status, 1))) break;
+          uint8_t* sA = smem + (size_t)stage * C::kStageBytes;
+          uint8_t* sB = sA + kABytes;
+          const int bcol = tile.col0 + rank * BNH;     // this CTA's share of the B columns
+          if (p.debug & 1) {   // results are garbage; only the timing of the remaining pipeline is of interest
+            if (rank == 0) mbar_arrive(&full[stage]);
+          } else if (CTAS == 2) {
+            // bytes of both CTAs are credited to the leader's barrier; only the leader arms it
+            const uint32_t lead_full = lead_full0 + 8u * (uint32_t)stage;
+            if (rank == 0) mbar_expect_tx(&full[stage], 2 * C::kStageBytes);
+            if (MODE == ESTMM) {
+              const int r = tile.row0 + kb * BLOCK_K;
 #pragma unroll
-          for (int c = 0; c < BLOCK_M / 64; ++c) tma_load_2d(sA + c * 8192, &tmA, &full[stage], tile.m0 + c * 64, r);
+              for (int c = 0; c < BLOCK_M / 64; ++c) tma_load_2d_pair(sA + c * 8192, &tmA, lead_full, tile.m0 + c * 64, r);
 #pragma unroll
-          for (int c = 0; c < BN / 64; ++c) tma_load_2d(sB + c * 8192, &tmB, &full[stage], tile.col0 + c * 64, r);
-        } else {
-          tma_load_2d(sA, &tmA, &full[stage], kb * BLOCK_K, tile.row0);
-          if (MODE == ESMM_NK) {
-            tma_load_3d(sB, &tmB, &full[stage], kb * BLOCK_K, tile.col0, tile.e);
+              for (int c = 0; c < BNH / 64; ++c) tma_load_2d_pair(sB + c * 8192, &tmB, lead_full, bcol + c * 64, r);
+            } else {
+              tma_load_2d_pair(sA, &tmA, lead_full, kb * BLOCK_K, tile.row0);
+              if (MODE == ESMM_NK) {
+                tma_load_3d_pair(sB, &tmB, lead_full, kb * BLOCK_K, bcol, tile.e);
+              } else {
+#pragma unroll
+                for (int c = 0; c < BNH / 64; ++c) tma_load_3d_pair(sB + c * 8192, &tmB, lead_full, bcol + c * 64, kb * BLOCK_K, tile.e);
+              }
+            }
           } else {
+            mbar_expect_tx(&full[stage], C::kStageBytes);
+            if (MODE == ESTMM) {
+              const int r = tile.row0 + kb * BLOCK_K;
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
-              tma_load_3d(sB + c * 8192, &tmB, &full[stage], tile.col0 + c * 64, kb * BLOCK_K, tile.e);
+              for (int c = 0; c < BLOCK_M / 64; ++c) tma_load_2d(sA + c * 8192, &tmA, &full[stage], tile.m0 + c * 64, r);
+#pragma unroll
+              for (int c = 0; c < BNH / 64; ++c) tma_load_2d(sB + c * 8192, &tmB, &full[stage], bcol + c * 64, r);
+            } else {
+              tma_load_2d(sA, &tmA, &full[stage], kb * BLOCK_K, tile.row0);
+              if (MODE == ESMM_NK) {
+                tma_load_3d(sB, &tmB, &full[stage], kb * BLOCK_K, bcol, tile.e);
+              } else {
+#pragma unroll
+                for (int c = 0; c < BNH / 64; ++c) tma_load_3d(sB + c * 8192, &tmB, &full[stage], bcol + c * 64, kb * BLOCK_K, tile.e);
+              }
+            }
           }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
-        ld.next(p);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
       constexpr bool kAMn = (MODE == ESTMM), kBMn = (MODE != ESMM_NK);
       // instruction descriptor: fp32 accumulate, A/B format (0 = f16, 1 = bf16), majors, N>>3, M>>4
+      // (M is 256 for a CTA pair: 128 rows from each CTA's shared memory into each CTA's TMEM)
       const uint32_t fmt = p.is_bf16 ? 1u : 0u;
       const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((kAMn ? 1u : 0u) << 15) | ((kBMn ? 1u : 0u) << 16) |
-                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((BLOCK_M * CTAS) >> 4) << 24);
       // K-major: 8-row groups 1024 B apart (SBO), LBO unused (1).  MN-major: 64-element column chunks
       // BLOCK_K*128 B apart (LBO), 8-k groups 1024 B apart (SBO).
-      uint32_t mn_lbo = BLOCK_K * 128, mn_sbo = 1024;
-      if (p.mn_swap) { uint32_t x = mn_lbo; mn_lbo = mn_sbo; mn_sbo = x; }
-      const uint32_t a_lbo = kAMn ? mn_lbo : 16, a_sbo = kAMn ? mn_sbo : 1024;
-      const uint32_t b_lbo = kBMn ? mn_lbo : 16, b_sbo = kBMn ? mn_sbo : 1024;
+      const uint32_t a_lbo = kAMn ? BLOCK_K * 128 : 16, b_lbo = kBMn ? BLOCK_K * 128 : 16;
       // start-address advance per K=16 step, in 16-byte units: 32 B inside the swizzle row (K-major)
       // or two 8-k groups = 2048 B (MN-major)
       const uint32_t a_step = kAMn ? (2048u >> 4) : (32u >> 4);
       const uint32_t b_step = kBMn ? (2048u >> 4) : (32u >> 4);
+      // The issuing thread is the pacemaker of the whole kernel: everything loop-invariant is hoisted so that a
+      // k-block costs one try_wait, two 64-bit adds, four MMAs and one commit.
+      const uint32_t s0 = smem_u32(smem);
+      const uint64_t adesc0 = make_smem_desc(s0, a_lbo, 1024);
+      const uint64_t bdesc0 = make_smem_desc(s0 + kABytes, b_lbo, 1024);
+      constexpr uint64_t kStageDesc = C::kStageBytes >> 4;    // descriptor start-address units per ring slot
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       Tile tile;
       int it = 0;
-      for (int64_t t = blockIdx.x; ok && get_tile<BN, MODE>(p, t, tile); t += gridDim.x, ++it) {
+      for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-        if (!(ok = mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, 2))) break;
+        if (!(ok = mbar_wait_fast(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, 2))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        uint32_t accumulate = 0;
         for (int kb = 0; kb < tile.num_kb; ++kb) {
-          if (!(ok = mbar_wait(&full[stage], phase, abort_flag, p.status, 3))) break;
-          tc_fence_after();
-          const uint32_t sA = smem_u32(smem + (size_t)stage * C::kStageBytes);
-          const uint64_t adesc = make_smem_desc(sA, a_lbo, a_sbo);
-          const uint64_t bdesc = make_smem_desc(sA + kABytes, b_lbo, b_sbo);
+          if (!(ok = mbar_wait_fast(&full[stage], phase, abort_flag, p.status, 3))) break;
+          const uint64_t adesc = adesc0 + (uint64_t)stage * kStageDesc;
+          const uint64_t bdesc = bdesc0 + (uint64_t)stage * kStageDesc;
+          if (!(p.debug & 2)) {
 #pragma unroll
-          for (int j = 0; j < BLOCK_K / UMMA_K; ++j)
-            umma_f16(d_tmem, adesc + (uint64_t)(j * a_step), bdesc + (uint64_t)(j * b_step), idesc, (kb | j) != 0 ? 1u : 0u);
-          umma_commit(&empty[stage]);  // slot reusable once these MMAs have read it
+            for (int j = 0; j < BLOCK_K / UMMA_K; ++j) {
+              if (CTAS == 2) umma_f16_pair(d_tmem, adesc + (uint64_t)(j * a_step), bdesc + (uint64_t)(j * b_step), idesc, j == 0 ? accumulate : 1u);
+              else umma_f16(d_tmem, adesc + (uint64_t)(j * a_step), bdesc + (uint64_t)(j * b_step), idesc, j == 0 ? accumulate : 1u);
+            }
+          }
+          accumulate = 1;
+          // slot reusable (in both CTAs) once these MMAs have read it
+          if (CTAS == 2) umma_commit_pair(&empty[stage]); else umma_commit(&empty[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        if (tile.num_kb > 0) umma_commit(&acc_full[acc]);
-        else mbar_arrive(&acc_full[acc]);  // empty segment: nothing to wait for, epilogue writes zeros
+        if (tile.num_kb > 0) {
+          if (CTAS == 2) umma_commit_pair(&acc_full[acc]); else umma_commit(&acc_full[acc]);
+        } else {  // empty segment: nothing to wait for, the epilogues write zeros
+          mbar_arrive(&acc_full[acc]);
+          if (CTAS == 2) mbar_arrive_cluster(map_to_cta(&acc_full[acc], 1));
+        }
       }
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue
-    constexpr int kParts = EPIW / 4;        // groups of four warps; each group owns BN / kParts columns of every tile
-    constexpr int kBufsPerPart = 4 / kParts;
+    // ------------------------------------------------------------------ epilogue (every CTA, its own 128 rows)
+    constexpr int kParts = kEpiWarps / 4;   // groups of four warps; each group owns BN / kParts columns of every tile
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
     const int part = (warp - 2) >> 2;
     const int is_bf16 = p.is_bf16;
     const bool leader = (q == 2) && lane == 0;   // the first warp of every group of four issues the group's TMA stores
-    uint32_t store_seq = 0;
+    uint8_t* buf = store_bufs + (size_t)part * C::kStoreBufBytes;
     bool ok = true;
     Tile tile;
     int it = 0;
-    for (int64_t t = blockIdx.x; ok && get_tile<BN, MODE>(p, t, tile); t += gridDim.x, ++it) {
+    for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
       if (!(ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4))) break;
@@ -471,7 +564,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int cc = 0; cc < BN / kParts / 32; ++cc) {
         const int cloc = part * (BN / kParts) + cc * 32;
         const int64_t gcol = (int64_t)tile.col0 + cloc;
-        if (gcol >= p.n) break;  // uniform across the warp
+        if (gcol >= p.n || !tile.valid) break;  // uniform across the four warps of a group
         uint32_t v[32];
         if (tile.num_kb > 0) {
           tmem_ld32(t_row + (uint32_t)cloc, v);
@@ -551,21 +644,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             case HEXA_EPI_DACT * 8 + HEXA_ACT_SILU: epi_values<HEXA_EPI_DACT, HEXA_ACT_SILU>(f, xp, live, ncols, is_bf16, yv, ov); break;
             default: epi_values<HEXA_EPI_LINEAR, HEXA_ACT_NONE>(f, xp, live, ncols, is_bf16, yv, ov); break;
           }
-          // registers -> swizzled staging tile -> one TMA store per 128x32 block (full 128-byte lines to L2);
-          // a group with two buffers alternates them, so at most one earlier store may still be reading
+          // registers -> swizzled staging tile -> one TMA store per 128x32 block (full 128-byte lines to L2)
           const bool two = (p.epilogue == HEXA_EPI_ACT) && p.aux != nullptr;
           for (int o = two ? 0 : 1; o < 2; ++o) {
-            if (p.direct_store) {
-              uint16_t* dst = reinterpret_cast<uint16_t*>(o == 0 ? p.aux : p.c) + r * (o == 0 ? p.ldaux : p.ldc) + gcol;
-              const uint32_t* w = o == 0 ? yv : ov;
-#pragma unroll
-              for (int g = 0; g < 4; ++g)
-                if (g * 8 < ncols) *reinterpret_cast<uint4*>(dst + g * 8) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
-              continue;
-            }
-            uint8_t* buf = store_bufs + (size_t)(part * kBufsPerPart + (store_seq % kBufsPerPart)) * C::kStoreBufBytes;
-            ++store_seq;
-            if (leader) bulk_wait_read<kBufsPerPart - 1>();
+            if (leader) bulk_wait_read<0>();   // the previous store has finished reading the buffer
             group_sync(1 + part);
             stage_row(buf, rloc, o == 0 ? yv : ov);
             fence_async_smem();
@@ -577,10 +659,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       }
-      // accumulator drained: hand it back to the MMA warp
+      // accumulator drained: hand it back to the (leader's) MMA warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (lane == 0) {
+        if (CTAS == 2 && rank != 0) mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
+        else mbar_arrive(&acc_empty[acc]);
+      }
     }
     if (leader) bulk_wait_all();   // staging buffers must outlive the stores that read them
   }
@@ -588,12 +673,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();   // no CTA leaves while its peer may still signal its barriers or read its shared memory
   if (warp == 1) {
     if (*abort_flag) {  // error path: give copies / MMAs in flight a bounded moment to land
       for (int i = 0; i < 64; ++i) __nanosleep(1000);
     }
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
+    if (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
   }
 }
 
@@ -631,21 +718,46 @@ int make_map(CUtensorMap* tm, const void* base, int is_bf16, int rank, const uin
   return HEXA_OK;
 }
 
-template <int BN, int MODE, int EPIW>
-int launch_w(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX, const Params& p,
-             int64_t max_tiles, cudaStream_t stream) {
-  using C = Cfg<BN>;
+template <int BN, int MODE, int CTAS>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX, const Params& p,
+           int64_t max_tiles, cudaStream_t stream) {
+  using C = Cfg<BN, CTAS>;
   static bool attr_set[64] = {false};
+  static int max_clusters[64] = {0};
+  auto kernel = gemm_tc_kernel<BN, MODE, CTAS>;
   int dev = 0;
   HEXA_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    HEXA_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, EPIW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
+  HEXA_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+  if (!attr_set[dev]) {
+    HEXA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
     attr_set[dev] = true;
   }
-  int64_t grid = max_tiles < sm_count() ? max_tiles : sm_count();
-  if (grid <= 0) return HEXA_OK;
-  gemm_tc_kernel<BN, MODE, EPIW><<<(unsigned)grid, 32 * (2 + EPIW), C::kSmemBytes, stream>>>(tmA, tmB, tmC, tmX, p);
-  HEXA_LAUNCH_CHECK("gemm_tc_kernel");
+  if (max_tiles <= 0) return HEXA_OK;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (CTAS == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (max_clusters[dev] == 0) {   // how many CTA pairs the device can hold at once (one CTA per SM)
+      cfg.gridDim = dim3(2 * (unsigned)(sm_count() / 2));
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = sm_count() / 2; }
+      max_clusters[dev] = n;
+    }
+    const int64_t pairs = max_tiles < max_clusters[dev] ? max_tiles : max_clusters[dev];
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+  } else {
+    cfg.gridDim = dim3((unsigned)(max_tiles < sm_count() ? max_tiles : sm_count()));
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, tmX, p);
+  if (e != cudaSuccess) {
+    set_error("launch of gemm_tc_kernel<%d,%d,%d> failed: %s", BN, MODE, CTAS, cudaGetErrorString(e));
+    return HEXA_ERR_CUDA;
+  }
   return HEXA_OK;
 }
 
@@ -653,27 +765,9 @@ int env_int(const char* name, int dflt) {
   const char* s = getenv(name);
   return s ? atoi(s) : dflt;
 }
-int epi_warps() { static int v = -1; if (v < 0) v = env_int("HEXA_EPI_WARPS", 16) == 8 ? 8 : 16; return v; }
-int direct_store_flag() { static int v = -1; if (v < 0) v = env_int("HEXA_DIRECT_STORE", 0) ? 1 : 0; return v; }
-
-template <int BN, int MODE>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX, const Params& p,
-           int64_t max_tiles, cudaStream_t stream) {
-  if (epi_warps() == 16) return launch_w<BN, MODE, 16>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
-  return launch_w<BN, MODE, 8>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
-}
-
-int prefetch_depth() {
-  static int v = -1;
-  if (v < 0) { const char* s = getenv("HEXA_L2_PREFETCH"); v = s ? atoi(s) : 0; if (v < 0 || v > 64) v = 0; }
-  return v;
-}
-
-int mn_swap_flag() {
-  static int v = -1;
-  if (v < 0) { const char* s = getenv("HEXA_DEBUG_MN_SWAP"); v = (s && s[0] == '1') ? 1 : 0; }
-  return v;
-}
+// HEXA_TC_CTAS=1 keeps every GEMM on single-CTA tiles (for A/B measurements); default: CTA pairs where they apply.
+int debug_flags() { static int v = -1; if (v < 0) v = env_int("HEXA_TC_DEBUG", 0); return v; }
+bool pairs_enabled() { static int v = -1; if (v < 0) v = env_int("HEXA_TC_CTAS", 2) == 1 ? 0 : 1; return v == 1; }
 
 }  // namespace
 
@@ -688,11 +782,13 @@ bool esmm_tc_supported(const void* a, int64_t lda, const void* b, int64_t ldb, i
 
 int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
                    const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
-                   const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token, int E,
-                   int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue, int act, cudaStream_t stream) {
+                   const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
+                   const int32_t* pair_block, int E, int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue,
+                   int act, cudaStream_t stream) {
   if (row_cap == 0) return HEXA_OK;
   const int is_bf16 = dtype == HEXA_BF16;
   const int BN = n_out > 128 ? 256 : 128;
+  const int ctas = (BN == 256 && pair_block != nullptr && pairs_enabled()) ? 2 : 1;
   CUtensorMap tmA, tmB;
   {
     uint64_t dims[2] = {(uint64_t)k, (uint64_t)row_cap};
@@ -704,7 +800,7 @@ int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int6
   if (b_layout == HEXA_B_NK) {
     uint64_t dims[3] = {(uint64_t)k, (uint64_t)n_out, (uint64_t)E};
     uint64_t str[2] = {(uint64_t)ldb * 2, (uint64_t)b_estride * 2};
-    uint32_t box[3] = {BLOCK_K, (uint32_t)BN, 1};
+    uint32_t box[3] = {BLOCK_K, (uint32_t)(BN / ctas), 1};   // each CTA of a pair loads half of the B rows
     int rc = make_map(&tmB, b, is_bf16, 3, dims, str, box);
     if (rc) return rc;
   } else {
@@ -731,15 +827,22 @@ int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int6
   }
   Params p{};
   p.tile_expert = tile_expert; p.pad_offsets = pad_offsets; p.row_token = row_token;
+  p.pair_block = pair_block; p.max_pairs = row_cap / (2 * BLOCK_M) + E;
   p.bias = bias; p.ldbias = ldbias; p.aux = aux; p.ldaux = ldaux; p.c = c; p.ldc = ldc;
   p.n = n_out; p.k = k; p.m = 0; p.E = E; p.epilogue = epilogue; p.act = act; p.is_bf16 = is_bf16;
-  p.mn_swap = mn_swap_flag(); p.prefetch = prefetch_depth(); p.direct_store = direct_store_flag(); p.status = status_word();
-  const int64_t max_tiles = (row_cap / BLOCK_M) * ceil_div(n_out, BN);
+  p.status = status_word(); p.debug = debug_flags();
+  const int64_t NT = ceil_div(n_out, BN);
+  if (ctas == 2) {
+    const int64_t max_tiles = p.max_pairs * NT;
+    return b_layout == HEXA_B_NK ? launch<256, ESMM_NK, 2>(tmA, tmB, tmC, tmX, p, max_tiles, stream)
+                                 : launch<256, ESMM_KN, 2>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
+  }
+  const int64_t max_tiles = (row_cap / BLOCK_M) * NT;
   if (b_layout == HEXA_B_NK)
-    return BN == 256 ? launch<256, ESMM_NK>(tmA, tmB, tmC, tmX, p, max_tiles, stream)
-                     : launch<128, ESMM_NK>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
-  return BN == 256 ? launch<256, ESMM_KN>(tmA, tmB, tmC, tmX, p, max_tiles, stream)
-                   : launch<128, ESMM_KN>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
+    return BN == 256 ? launch<256, ESMM_NK, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream)
+                     : launch<128, ESMM_NK, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
+  return BN == 256 ? launch<256, ESMM_KN, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream)
+                   : launch<128, ESMM_KN, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
 }
 
 bool estmm_tc_supported(const void* p, int64_t ldp, const void* q, int64_t ldq, const void* out, int64_t ldo,
@@ -757,6 +860,7 @@ int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, con
                     int out_dtype, int beta, cudaStream_t stream) {
   const int is_bf16 = dtype == HEXA_BF16;
   const int BN = n > 128 ? 256 : 128;
+  const int ctas = (BN == 256 && m > BLOCK_M && pairs_enabled()) ? 2 : 1;
   CUtensorMap tmA, tmB;
   // the maps need at least one row even when no token was routed
   const uint64_t rows = row_cap > 0 ? (uint64_t)row_cap : 1;
@@ -776,12 +880,13 @@ int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, con
   }
   Params p{};
   p.pad_offsets = pad_offsets; p.c = out; p.ldc = ldo; p.c_estride = o_estride; p.n = n; p.m = m; p.E = E;
-  p.is_bf16 = is_bf16; p.out_f32 = out_dtype == HEXA_F32; p.beta = beta; p.mn_swap = mn_swap_flag();
-  p.prefetch = prefetch_depth(); p.status = status_word();
-  const int64_t max_tiles = (int64_t)E * ceil_div(m, BLOCK_M) * ceil_div(n, BN);
+  p.is_bf16 = is_bf16; p.out_f32 = out_dtype == HEXA_F32; p.beta = beta;
+  p.status = status_word(); p.debug = debug_flags();
+  const int64_t max_tiles = (int64_t)E * ceil_div(m, BLOCK_M * ctas) * ceil_div(n, BN);
   // ESTMM stores straight from registers; the two output maps are unused placeholders
-  return BN == 256 ? launch<256, ESTMM>(tmA, tmB, tmA, tmA, p, max_tiles, stream)
-                   : launch<128, ESTMM>(tmA, tmB, tmA, tmA, p, max_tiles, stream);
+  if (ctas == 2) return launch<256, ESTMM, 2>(tmA, tmB, tmA, tmA, p, max_tiles, stream);
+  return BN == 256 ? launch<256, ESTMM, 1>(tmA, tmB, tmA, tmA, p, max_tiles, stream)
+                   : launch<128, ESTMM, 1>(tmA, tmB, tmA, tmA, p, max_tiles, stream);
 }
 
 }  // namespace hexa

@@ -100,11 +100,16 @@ __device__ __forceinline__ float act_grad(int act, float x) {
 // Accurate to ~2e-7 absolute, far below bf16/fp16 resolution, at roughly a third of the instructions
 // of erff/expf: erf by Abramowitz-Stegun 7.1.26 (one reciprocal, one exp2, a degree-5 Horner), with
 // exp(-x^2/2) shared between the Gaussian CDF and PDF.  ACT is a compile-time HEXA_ACT_* id.
+__device__ __forceinline__ float rcp_fast(float x) {   // one MUFU.RCP, ~1 ulp; __frcp_rn would add a Newton step
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void gelu_parts(float x, float& s, float& e) {
   // s = 1 + erf(x / sqrt2) (so gelu = 0.5 x s), e = exp(-x^2 / 2)
   e = __expf(-0.5f * x * x);
   const float z = fabsf(x) * 0.70710678118654752f;
-  const float t = __frcp_rn(fmaf(0.3275911f, z, 1.0f));
+  const float t = rcp_fast(fmaf(0.3275911f, z, 1.0f));
   float q = fmaf(1.061405429f, t, -1.453152027f);
   q = fmaf(q, t, 1.421413741f);
   q = fmaf(q, t, -0.284496736f);
@@ -122,7 +127,7 @@ template <int ACT> __device__ __forceinline__ float act_fast(float x) {
   if (ACT == HEXA_ACT_RELU) return fmaxf(x, 0.f);
   if (ACT == HEXA_ACT_GELU) { float s, e; gelu_parts(x, s, e); return 0.5f * x * s; }
   if (ACT == HEXA_ACT_GELU_TANH) return 0.5f * x * (1.f + tanh_fast(0.7978845608028654f * fmaf(0.044715f * x * x, x, x)));
-  if (ACT == HEXA_ACT_SILU) return x * __frcp_rn(1.f + __expf(-x));
+  if (ACT == HEXA_ACT_SILU) return x * rcp_fast(1.f + __expf(-x));
   return x;
 }
 template <int ACT> __device__ __forceinline__ float act_grad_fast(float x) {
@@ -134,7 +139,7 @@ template <int ACT> __device__ __forceinline__ float act_grad_fast(float x) {
     const float du = 0.7978845608028654f * fmaf(3.f * 0.044715f, x2, 1.f);
     return fmaf(0.5f * x * (1.f - t * t), du, 0.5f * (1.f + t));
   }
-  if (ACT == HEXA_ACT_SILU) { const float sg = __frcp_rn(1.f + __expf(-x)); return sg * fmaf(x, 1.f - sg, 1.f); }
+  if (ACT == HEXA_ACT_SILU) { const float sg = rcp_fast(1.f + __expf(-x)); return sg * fmaf(x, 1.f - sg, 1.f); }
   return 1.f;
 }
 

@@ -10,8 +10,8 @@ int estmm_simt_launch(const void*, int64_t, const void*, int64_t, const int32_t*
 bool esmm_tc_supported(const void*, int64_t, const void*, int64_t, int64_t, const void*, int64_t, const void*, int64_t,
                        const float*, int64_t, int64_t, int);
 int esmm_tc_launch(const void*, int64_t, const void*, int, int64_t, int64_t, const float*, int64_t, void*, int64_t, void*,
-                   int64_t, const int32_t*, const int32_t*, const int32_t*, int, int64_t, int64_t, int64_t, int, int, int,
-                   cudaStream_t);
+                   int64_t, const int32_t*, const int32_t*, const int32_t*, const int32_t*, int, int64_t, int64_t, int64_t, int,
+                   int, int, cudaStream_t);
 bool estmm_tc_supported(const void*, int64_t, const void*, int64_t, const void*, int64_t, int64_t, int64_t, int, int);
 int estmm_tc_launch(const void*, int64_t, const void*, int64_t, const int32_t*, int, int64_t, int64_t, int64_t, void*, int64_t,
                     int64_t, int, int, int, cudaStream_t);
@@ -21,9 +21,9 @@ using namespace hexa;
 
 extern "C" int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
                          const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
-                         const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token, int E,
-                         int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue, int act, int engine,
-                         void* stream_) {
+                         const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
+                         const int32_t* pair_block, int E, int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue,
+                         int act, int engine, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   HEXA_REQUIRE(a && b && c && tile_expert && pad_offsets, "hexa_esmm: null pointer");
   HEXA_REQUIRE(E > 0 && row_cap >= 0 && row_cap % kRowTile == 0 && n_out > 0 && k > 0,
@@ -43,7 +43,7 @@ extern "C" int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout
   }
   if (engine != HEXA_ENGINE_SIMT && tc_ok)
     return esmm_tc_launch(a, lda, b, b_layout, ldb, b_estride, bias, ldbias, aux, ldaux, c, ldc, tile_expert, pad_offsets,
-                          row_token, E, row_cap, n_out, k, dtype, epilogue, act, stream);
+                          row_token, pair_block, E, row_cap, n_out, k, dtype, epilogue, act, stream);
   return esmm_simt_launch(a, lda, b, b_layout, ldb, b_estride, bias, ldbias, aux, ldaux, c, ldc, tile_expert, pad_offsets,
                           row_token, E, row_cap, n_out, k, dtype, epilogue, act, stream);
 }

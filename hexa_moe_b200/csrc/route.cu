@@ -46,7 +46,8 @@ __global__ void route_hist(const int32_t* __restrict__ ids, int64_t T, int64_t n
 __global__ void __launch_bounds__(1024)
 route_scan(int32_t* __restrict__ chunk_hist, int64_t n_chunks, int E, int align, int64_t row_capacity,
            int32_t* __restrict__ counts, int32_t* __restrict__ seg_offsets, int32_t* __restrict__ pad_offsets,
-           int32_t* __restrict__ row_token, int32_t* __restrict__ tile_expert) {
+           int32_t* __restrict__ row_token, int32_t* __restrict__ tile_expert, int32_t* __restrict__ pair_off,
+           int32_t* __restrict__ pair_block, int64_t pair_cap) {
   extern __shared__ int32_t sm[];
   int32_t* s_cnt = sm;          // [E]
   int32_t* s_pad = sm + E;      // [E + 1]
@@ -73,33 +74,49 @@ route_scan(int32_t* __restrict__ chunk_hist, int64_t n_chunks, int E, int align,
   // exclusive scans over experts (unpadded and padded) by warp 0, 32 experts per step
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
-    int32_t carry_seg = 0, carry_pad = 0;
+    int32_t carry_seg = 0, carry_pad = 0, carry_pair = 0;
     for (int base = 0; base < E; base += 32) {
       int e = base + lane;
       int32_t c = e < E ? s_cnt[e] : 0;
       int32_t p = (c + align - 1) / align * align;
-      int32_t ic = c, ip = p;
+      int32_t q = (p / kRowTile + 1) / 2;      // pair tiles: two 128-row blocks each, the last one may be half empty
+      int32_t ic = c, ip = p, iq = q;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         int32_t tc = __shfl_up_sync(0xffffffffu, ic, o), tp = __shfl_up_sync(0xffffffffu, ip, o);
-        if (lane >= o) { ic += tc; ip += tp; }
+        int32_t tq = __shfl_up_sync(0xffffffffu, iq, o);
+        if (lane >= o) { ic += tc; ip += tp; iq += tq; }
       }
       if (e < E) {
         seg_offsets[e] = carry_seg + ic - c;
         int32_t po = carry_pad + ip - p;
         pad_offsets[e] = po;
         s_pad[e] = po;
+        if (pair_block) pair_off[e] = carry_pair + iq - q;
       }
       carry_seg += __shfl_sync(0xffffffffu, ic, 31);
       carry_pad += __shfl_sync(0xffffffffu, ip, 31);
+      carry_pair += __shfl_sync(0xffffffffu, iq, 31);
     }
     if (lane == 0) {
       seg_offsets[E] = carry_seg;
       pad_offsets[E] = carry_pad;
       s_pad[E] = carry_pad;
+      if (pair_block) pair_off[E] = carry_pair;
     }
   }
   __syncthreads();
+  // pair-tile list for CTA-pair GEMMs: entry = (first 128-row block) * 2 + (the next block belongs to the same expert)
+  if (pair_block) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      const int32_t b0 = s_pad[e] / kRowTile, nb = (s_pad[e + 1] - s_pad[e]) / kRowTile;
+      int32_t o = pair_off[e];
+      for (int32_t i = 0; i < nb; i += 2, ++o)
+        if (o < pair_cap) pair_block[o] = (b0 + i) * 2 + (i + 1 < nb ? 1 : 0);
+    }
+    const int32_t total = pair_off[E];
+    for (int64_t i = total + threadIdx.x; i < pair_cap; i += blockDim.x) pair_block[i] = -1;
+  }
   // tile -> expert: binary search for the segment that holds the tile's first row
   const int64_t n_tiles = row_capacity / align;
   const int32_t n_pad = s_pad[E];
@@ -207,13 +224,19 @@ extern "C" size_t hexa_route_workspace_bytes(int64_t T, int top_k, int E) {
   if (T < 0 || top_k <= 0 || E <= 0) return 0;
   int64_t chunks = ceil_div(T * top_k, kRowsPerWarp);
   if (chunks < 1) chunks = 1;
-  return (size_t)chunks * (size_t)E * sizeof(int32_t);
+  return ((size_t)chunks * (size_t)E + (size_t)E + 1) * sizeof(int32_t);   // per-chunk histograms + pair-tile offsets
+}
+
+extern "C" int64_t hexa_route_pair_capacity(int64_t T, int top_k, int E) {
+  const int64_t cap = hexa_route_row_capacity(T, top_k, E, kRowTile);
+  if (cap < 0) return -1;
+  return cap / (2 * kRowTile) + E + 1;   // every expert may end on a half-filled pair; one terminator
 }
 
 extern "C" int hexa_route(const int32_t* ids, int64_t T, int top_k, int64_t stride_t, int64_t stride_k, int E,
                           int align, int32_t* counts, int32_t* seg_offsets, int32_t* pad_offsets,
-                          int32_t* row_token, int32_t* token_row, int32_t* tile_expert, void* workspace,
-                          size_t workspace_bytes, void* stream_) {
+                          int32_t* row_token, int32_t* token_row, int32_t* tile_expert, int32_t* pair_block,
+                          void* workspace, size_t workspace_bytes, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   HEXA_REQUIRE(T >= 0 && top_k > 0 && E > 0 && E <= kMaxExperts && align > 0, "hexa_route: bad sizes T=%lld k=%d E=%d align=%d",
                (long long)T, top_k, E, align);
@@ -238,8 +261,11 @@ extern "C" int hexa_route(const int32_t* ids, int64_t T, int top_k, int64_t stri
                                                                                 chunk_hist);
     HEXA_LAUNCH_CHECK("route_hist");
   }
-  route_scan<<<1, 1024, (2 * (size_t)E + 1) * sizeof(int32_t), stream>>>(chunk_hist, n_chunks, E, align, row_cap, counts,
-                                                                         seg_offsets, pad_offsets, row_token, tile_expert);
+  HEXA_REQUIRE(pair_block == nullptr || align == kRowTile, "hexa_route: the pair-tile list needs align = %d", kRowTile);
+  int32_t* pair_off = chunk_hist + (size_t)(n_chunks > 0 ? n_chunks : 1) * E;
+  route_scan<<<1, 1024, (2 * (size_t)E + 1) * sizeof(int32_t), stream>>>(
+      chunk_hist, n_chunks, E, align, row_cap, counts, seg_offsets, pad_offsets, row_token, tile_expert, pair_off, pair_block,
+      pair_block ? hexa_route_pair_capacity(T, top_k, E) : 0);
   HEXA_LAUNCH_CHECK("route_scan");
   if (n_chunks > 0) {
     route_scatter<<<(unsigned)ceil_div(n_chunks, warps), warps * 32, smem, stream>>>(

@@ -55,6 +55,7 @@ class Routing:
     row_token: torch.Tensor     # [row_capacity] token of each sorted row, -1 for pad rows
     token_row: torch.Tensor     # [T*k] sorted row of routed row (t, j) at t*k + j
     tile_expert: torch.Tensor   # [row_capacity/align]
+    pair_block: Optional[torch.Tensor]   # pair-tile list for the two-CTA GEMMs (align = 128 only)
     num_tokens: int
     top_k: int
     num_experts: int
@@ -80,14 +81,16 @@ def route(ids: torch.Tensor, num_experts: int, align: int = L.ROW_TILE, route_ma
     if cap < 0:
         raise L.HexaError("route: bad sizes")
     i32 = dict(dtype=torch.int32, device=dev)
+    pairs = torch.empty(lib().hexa_route_pair_capacity(T, k, num_experts), **i32) if align == L.ROW_TILE else None
     r = Routing(torch.empty(num_experts, **i32), torch.empty(num_experts + 1, **i32), torch.empty(num_experts + 1, **i32),
                 torch.empty(max(cap, 1), **i32), torch.empty(max(T * k, 1), **i32), torch.empty(max(cap // align, 1), **i32),
-                T, k, num_experts, align, cap)
+                pairs, T, k, num_experts, align, cap)
     ws_bytes = lib().hexa_route_workspace_bytes(T, k, num_experts)
     ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
     with _Timed("route", 12.0 * T * k):
         check(lib().hexa_route(ptr(ids), T, k, st, sk, num_experts, align, ptr(r.counts), ptr(r.seg_offsets), ptr(r.pad_offsets),
-                               ptr(r.row_token), ptr(r.token_row), ptr(r.tile_expert), ptr(ws), ws.numel(), s), "hexa_route")
+                               ptr(r.row_token), ptr(r.token_row), ptr(r.tile_expert), ptr(r.pair_block), ptr(ws), ws.numel(), s),
+              "hexa_route")
     return r
 
 
@@ -144,7 +147,8 @@ def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Opti
     with _Timed("esmm:%d" % epilogue, 2.0 * r.num_tokens * r.top_k * n_out * k):
         check(lib().hexa_esmm(ptr(a), _ld(a), ptr(b), b_layout, b.stride(1), b.stride(0), ptr(bias),
                               0 if bias is None else _ld(bias), ptr(aux), 0 if aux is None else _ld(aux), ptr(out), _ld(out),
-                              ptr(r.tile_expert), ptr(r.pad_offsets), ptr(r.row_token), r.num_experts, r.row_capacity, n_out, k,
+                              ptr(r.tile_expert), ptr(r.pad_offsets), ptr(r.row_token), ptr(r.pair_block), r.num_experts, r.row_capacity,
+                              n_out, k,
                               dt(a), epilogue, act, engine, stream_of(a)), "hexa_esmm")
     return out
 

@@ -87,16 +87,21 @@ int hexa_set_status_word(int32_t* status);
 /* Upper bound on padded rows: T*top_k + E*(align-1), rounded up to a multiple of align. */
 int64_t hexa_route_row_capacity(int64_t num_tokens, int top_k, int num_experts, int align);
 size_t hexa_route_workspace_bytes(int64_t num_tokens, int top_k, int num_experts);
+/* Entries of the optional pair-tile list (align = 128 only): row_capacity/256 + E + 1. */
+int64_t hexa_route_pair_capacity(int64_t num_tokens, int top_k, int num_experts);
 
 /* ids: expert id of routed row (t,j) at ids[t*stride_t + j*stride_k]; ids outside [0,E) are
  * skipped (their token_row entry is -1).
  * Outputs (device, int32): counts[E], seg_offsets[E+1] (exclusive scan of counts),
  * pad_offsets[E+1], row_token[row_capacity], token_row[T*top_k], tile_expert[row_capacity/align]
- * (-1 beyond pad_offsets[E]).  Results are deterministic: identical to a stable sort. */
+ * (-1 beyond pad_offsets[E]).  Results are deterministic: identical to a stable sort.
+ * pair_block (optional, NULL to skip; needs align = 128): for the GEMMs that run on pairs of SMs, the list of
+ * 256-row pair tiles, entry = (first 128-row block)*2 + (1 if the next block belongs to the same expert),
+ * terminated and padded with -1; hexa_route_pair_capacity entries. */
 int hexa_route(const int32_t* ids, int64_t num_tokens, int top_k, int64_t stride_t, int64_t stride_k,
                int num_experts, int align, int32_t* counts, int32_t* seg_offsets, int32_t* pad_offsets,
-               int32_t* row_token, int32_t* token_row, int32_t* tile_expert, void* workspace,
-               size_t workspace_bytes, void* stream);
+               int32_t* row_token, int32_t* token_row, int32_t* tile_expert, int32_t* pair_block,
+               void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- row movement between token order and sorted-row order (the reference gathers rows by
  *      tok_ids inside its kernels, kernels/esmm.py:95-101, and sums the k routes in Python,
@@ -118,12 +123,14 @@ int hexa_combine_rows(const void* src, int64_t src_ld, const int32_t* token_row,
  *   acc[r,:] = a[r,:] (1 x k) times b[e] (layout per b_layout), fp32 accumulation, then `epilogue`.
  * a [row_capacity, k] (lda), c [row_capacity, n_out] (ldc), aux like c (ldaux) or NULL,
  * bias fp32 [E, n_out] (ldbias) or NULL, b expert stride b_estride and row stride ldb in elements.
- * Rows with row_token[r] < 0 are written as zeros.  Segments must be aligned to 128 rows. */
+ * Rows with row_token[r] < 0 are written as zeros.  Segments must be aligned to 128 rows.
+ * pair_block: the list hexa_route produced, or NULL; with it (and n_out > 128, 16-bit data) the tcgen05 kernel
+ * runs on clusters of two CTAs (256-row tiles, each CTA loading half of the weight tile). */
 int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
               const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
               const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
-              int num_experts, int64_t row_capacity, int64_t n_out, int64_t k, int dtype, int epilogue,
-              int act, int engine, void* stream);
+              const int32_t* pair_block, int num_experts, int64_t row_capacity, int64_t n_out, int64_t k,
+              int dtype, int epilogue, int act, int engine, void* stream);
 
 /* ---- ESTMM: replaces task 1 of launch_fused_grad_* (include/hexa_moe.h:74-181),
  *      kernels/fused.py:183-235 (operator definition; the reference kernels mis-handle segments

@@ -97,8 +97,15 @@ def route(ids: torch.Tensor, num_exps: int, align: int):
         token_row[(f % T) * k + (f // T)] = rows.astype(np.int32)
         tile_expert[pad[e] // align: pad[e + 1] // align] = e
     tt = lambda a: torch.from_numpy(np.asarray(a).astype(np.int32))
+    # pair tiles for GEMMs that run on two SMs (not in the reference): two consecutive 128-row blocks of one
+    # expert; entry = first_block * 2 + (second block belongs to the same expert)
+    pairs = []
+    if align == 128:
+        for e in range(num_exps):
+            b0, nb = int(pad[e]) // 128, int(padc[e]) // 128
+            pairs += [(b0 + i) * 2 + (1 if i + 1 < nb else 0) for i in range(0, nb, 2)]
     return dict(counts=tt(counts), seg_offsets=tt(seg), pad_offsets=tt(pad), row_token=tt(row_token),
-                token_row=tt(token_row), tile_expert=tt(tile_expert), n_pad=n_pad)
+                token_row=tt(token_row), tile_expert=tt(tile_expert), n_pad=n_pad, pair_block=tt(pairs))
 
 
 # --------------------------------------------------------------------------------------------

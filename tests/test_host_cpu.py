@@ -33,7 +33,8 @@ def test_library_exports_every_declared_symbol():
     h = _lib.lib()
     assert h.hexa_version() >= 100
     assert h.hexa_route_row_capacity(1000, 2, 8, 128) == (2000 + 8 * 127 + 127) // 128 * 128
-    assert h.hexa_route_workspace_bytes(1000, 2, 8) == 4 * 8 * 4
+    assert h.hexa_route_workspace_bytes(1000, 2, 8) == (4 * 8 + 8 + 1) * 4
+    assert h.hexa_route_pair_capacity(1000, 2, 8) == h.hexa_route_row_capacity(1000, 2, 8, 128) // 256 + 8 + 1
     assert h.hexa_ess_workspace_bytes(1024, 100) == 8 * 100 * 4
     assert h.hexa_route_row_capacity(10, 0, 8, 128) == -1
 
@@ -41,9 +42,9 @@ def test_library_exports_every_declared_symbol():
 def test_argument_errors_come_back_as_status_codes():
     from hexa_moe_b200 import _lib
     h = _lib.lib()
-    rc = h.hexa_route(None, 10, 1, 1, 10, 4, 128, None, None, None, None, None, None, None, 0, None)
+    rc = h.hexa_route(None, 10, 1, 1, 10, 4, 128, None, None, None, None, None, None, None, None, 0, None)
     assert rc == -1 and b"null" in h.hexa_last_error_string()
-    rc = h.hexa_esmm(None, 0, None, 0, 0, 0, None, 0, None, 0, None, 0, None, None, None, 4, 128, 8, 8, 2, 0, 0, 0, None)
+    rc = h.hexa_esmm(None, 0, None, 0, 0, 0, None, 0, None, 0, None, 0, None, None, None, None, 4, 128, 8, 8, 2, 0, 0, 0, None)
     assert rc == -1
 
 

@@ -65,6 +65,12 @@ def test_route_bit_exact(ops, T, k, E, align):
     te = r.tile_expert.cpu()
     assert torch.equal(te[: n_pad // align], want["tile_expert"])
     assert (te[n_pad // align: r.row_capacity // align] == -1).all()
+    if align == 128:
+        pb = r.pair_block.cpu()
+        n_pairs = want["pair_block"].numel()
+        assert torch.equal(pb[:n_pairs], want["pair_block"]) and (pb[n_pairs:] == -1).all() and pb.numel() > n_pairs
+    else:
+        assert r.pair_block is None
     # route-major ids ([k, T]) give the same answer
     r2 = ops.route(ids.t().contiguous().cuda(), E, align, route_major=True)
     assert torch.equal(r2.row_token.cpu()[:n_pad], want["row_token"])
