@@ -182,6 +182,9 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # the collectives overlap the persistent GEMM kernels: keep NCCL to a few CTAs (NVSwitch needs few to
+        # saturate the links) so the SMs the GEMMs leave free (HEXA_COMM_SMS) are enough for it
+        os.environ.setdefault("NCCL_MAX_CTAS", "16")
         dist.init_process_group("nccl", device_id=dev)
     n_gpus = world
 

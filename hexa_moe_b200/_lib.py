@@ -30,6 +30,7 @@ SIGNATURES = {
     "hexa_version": (ci, []),
     "hexa_last_error_string": (C.c_char_p, []),
     "hexa_set_status_word": (ci, [vp]),
+    "hexa_set_sm_limit": (ci, [ci]),
     "hexa_route_row_capacity": (i64, [i64, ci, ci, ci]),
     "hexa_route_workspace_bytes": (sz, [i64, ci, ci]),
     "hexa_route_pair_capacity": (i64, [i64, ci, ci]),
@@ -37,7 +38,8 @@ SIGNATURES = {
     "hexa_gather_rows": (ci, [vp, i64, vp, vp, ci, i64, i64, vp, i64, ci, vp]),
     "hexa_combine_rows": (ci, [vp, i64, vp, i64, ci, i64, vp, i64, ci, vp]),
     "hexa_esmm": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, vp, i64, vp, i64, vp, vp, vp, vp, ci, i64, i64, i64, ci, ci, ci, ci, vp]),
-    "hexa_estmm": (ci, [vp, i64, vp, i64, vp, ci, i64, i64, i64, vp, i64, i64, ci, ci, ci, ci, vp]),
+    "hexa_estmm": (ci, [vp, i64, vp, i64, vp, ci, i64, i64, i64, vp, i64, i64, i64, i64, ci, ci, ci, ci, vp]),
+    "hexa_copy_2d": (ci, [vp, i64, vp, i64, i64, i64, vp]),
     "hexa_ess_workspace_bytes": (sz, [i64, i64]),
     "hexa_ess": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, ci, vp, sz, vp]),
     "hexa_mask_pad_rows": (ci, [vp, i64, vp, vp, ci, i64, i64, ci, vp]),

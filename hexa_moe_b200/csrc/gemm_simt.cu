@@ -96,7 +96,7 @@ template <typename T, typename TO>
 __global__ void __launch_bounds__(256)
 estmm_simt_kernel(const T* __restrict__ p, int64_t ldp, const T* __restrict__ q, int64_t ldq,
                   const int32_t* __restrict__ pad_offsets, int64_t m, int64_t n, TO* __restrict__ out, int64_t ldo,
-                  int64_t o_estride, int beta) {
+                  int64_t o_estride, int64_t m_split, int64_t split_stride, int beta) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
   const int e = blockIdx.z;
@@ -146,8 +146,9 @@ estmm_simt_kernel(const T* __restrict__ p, int64_t ldp, const T* __restrict__ q,
       const int64_t nn = n0 + tx * 4 + j;
       if (nn >= n) continue;
       float v = acc[i][j];
-      if (beta) v += to_f32<TO>(oe[mm * ldo + nn]);
-      oe[mm * ldo + nn] = from_f32<TO>(v);
+      TO* dst = oe + (mm / m_split) * split_stride + (mm % m_split) * ldo + nn;
+      if (beta) v += to_f32<TO>(*dst);
+      *dst = from_f32<TO>(v);
     }
   }
 }
@@ -177,13 +178,13 @@ int esmm_simt_launch(const void* a, int64_t lda, const void* b, int b_layout, in
 }
 
 int estmm_simt_launch(const void* p, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets, int E,
-                      int64_t m, int64_t n, void* out, int64_t ldo, int64_t o_estride, int dtype, int out_dtype,
-                      int beta, cudaStream_t stream) {
+                      int64_t m, int64_t n, void* out, int64_t ldo, int64_t o_estride, int64_t m_split, int64_t split_stride,
+                      int dtype, int out_dtype, int beta, cudaStream_t stream) {
   dim3 grid((unsigned)ceil_div(n, BN), (unsigned)ceil_div(m, BM), (unsigned)E);
   HEXA_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "hexa_estmm (simt): grid too large");
 #define HEXA_ESTMM_SIMT(T, TO)                                                                                       \
   estmm_simt_kernel<T, TO><<<grid, 256, 0, stream>>>((const T*)p, ldp, (const T*)q, ldq, pad_offsets, m, n, (TO*)out, \
-                                                     ldo, o_estride, beta)
+                                                     ldo, o_estride, m_split, split_stride, beta)
   if (dtype == HEXA_F32 && out_dtype == HEXA_F32) HEXA_ESTMM_SIMT(float, float);
   else if (dtype == HEXA_F16 && out_dtype == HEXA_F32) HEXA_ESTMM_SIMT(__half, float);
   else if (dtype == HEXA_F16 && out_dtype == HEXA_F16) HEXA_ESTMM_SIMT(__half, __half);

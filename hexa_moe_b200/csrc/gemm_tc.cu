@@ -59,6 +59,7 @@ struct Params {
   void* c;          // ESMM: c ; ESTMM: out
   int64_t ldc;
   int64_t c_estride;  // ESTMM only
+  int64_t m_split, split_stride;  // ESTMM: output row m lives at (m / m_split) * split_stride + (m % m_split) * ldc
   int64_t n;        // output columns
   int64_t k;        // ESMM: contraction length ; ESTMM: unused
   int64_t m;        // ESTMM: output rows per expert
@@ -576,7 +577,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int64_t mrow = (int64_t)tile.m0 + rloc;
           if (mrow < p.m) {
             if (p.out_f32) {
-              float* o = reinterpret_cast<float*>(p.c) + (int64_t)tile.e * p.c_estride + mrow * p.ldc + gcol;
+              float* o = reinterpret_cast<float*>(p.c) + (int64_t)tile.e * p.c_estride + (mrow / p.m_split) * p.split_stride + (mrow % p.m_split) * p.ldc + gcol;
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
                 if (gcol + g * 4 < p.n) {
@@ -590,7 +591,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
               }
             } else {
-              uint16_t* o = reinterpret_cast<uint16_t*>(p.c) + (int64_t)tile.e * p.c_estride + mrow * p.ldc + gcol;
+              uint16_t* o = reinterpret_cast<uint16_t*>(p.c) + (int64_t)tile.e * p.c_estride + (mrow / p.m_split) * p.split_stride + (mrow % p.m_split) * p.ldc + gcol;
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
                 if (gcol + g * 8 < p.n) {
@@ -748,10 +749,13 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
       if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) { (void)cudaGetLastError(); n = sm_count() / 2; }
       max_clusters[dev] = n;
     }
-    const int64_t pairs = max_tiles < max_clusters[dev] ? max_tiles : max_clusters[dev];
-    cfg.gridDim = dim3((unsigned)(2 * pairs));
+    int64_t pairs = max_tiles < max_clusters[dev] ? max_tiles : max_clusters[dev];
+    if (sm_limit() > 0 && pairs > sm_limit() / 2) pairs = sm_limit() / 2;
+    cfg.gridDim = dim3((unsigned)(2 * (pairs > 0 ? pairs : 1)));
   } else {
-    cfg.gridDim = dim3((unsigned)(max_tiles < sm_count() ? max_tiles : sm_count()));
+    int64_t ctas = max_tiles < sm_count() ? max_tiles : sm_count();
+    if (sm_limit() > 0 && ctas > sm_limit()) ctas = sm_limit();
+    cfg.gridDim = dim3((unsigned)ctas);
   }
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, tmX, p);
   if (e != cudaSuccess) {
@@ -846,18 +850,18 @@ int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int6
 }
 
 bool estmm_tc_supported(const void* p, int64_t ldp, const void* q, int64_t ldq, const void* out, int64_t ldo,
-                        int64_t o_estride, int64_t n, int dtype, int out_dtype) {
+                        int64_t o_estride, int64_t split_stride, int64_t n, int dtype, int out_dtype) {
   if (dtype != HEXA_F16 && dtype != HEXA_BF16) return false;
   if (out_dtype != HEXA_F32 && out_dtype != dtype) return false;
   if (!aligned16(p) || !aligned16(q) || !aligned16(out)) return false;
   const int ov = out_dtype == HEXA_F32 ? 4 : 8;
-  if (ldp % 8 || ldq % 8 || ldo % ov || o_estride % ov || n % 8) return false;
+  if (ldp % 8 || ldq % 8 || ldo % ov || o_estride % ov || split_stride % ov || n % 8) return false;
   return true;
 }
 
 int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets, int E,
-                    int64_t row_cap, int64_t m, int64_t n, void* out, int64_t ldo, int64_t o_estride, int dtype,
-                    int out_dtype, int beta, cudaStream_t stream) {
+                    int64_t row_cap, int64_t m, int64_t n, void* out, int64_t ldo, int64_t o_estride, int64_t m_split,
+                    int64_t split_stride, int dtype, int out_dtype, int beta, cudaStream_t stream) {
   const int is_bf16 = dtype == HEXA_BF16;
   const int BN = n > 128 ? 256 : 128;
   const int ctas = (BN == 256 && m > BLOCK_M && pairs_enabled()) ? 2 : 1;
@@ -880,6 +884,7 @@ int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, con
   }
   Params p{};
   p.pad_offsets = pad_offsets; p.c = out; p.ldc = ldo; p.c_estride = o_estride; p.n = n; p.m = m; p.E = E;
+  p.m_split = m_split; p.split_stride = split_stride;
   p.is_bf16 = is_bf16; p.out_f32 = out_dtype == HEXA_F32; p.beta = beta;
   p.status = status_word(); p.debug = debug_flags();
   const int64_t max_tiles = (int64_t)E * ceil_div(m, BLOCK_M * ctas) * ceil_div(n, BN);

@@ -45,6 +45,7 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline size_t dtype_size(int dt) { return dt == HEXA_F32 ? 4 : 2; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 int sm_count();  // SMs of the current device (cached per device)
+int sm_limit();  // upper bound on the SMs persistent kernels may occupy (0 = all), see hexa_set_sm_limit
 
 constexpr int kRowTile = 128;  // rows per GEMM tile == required segment alignment of the GEMM operators
 

@@ -6,15 +6,15 @@ int esmm_simt_launch(const void*, int64_t, const void*, int, int64_t, int64_t, c
                      int64_t, const int32_t*, const int32_t*, const int32_t*, int, int64_t, int64_t, int64_t, int, int, int,
                      cudaStream_t);
 int estmm_simt_launch(const void*, int64_t, const void*, int64_t, const int32_t*, int, int64_t, int64_t, void*, int64_t,
-                      int64_t, int, int, int, cudaStream_t);
+                      int64_t, int64_t, int64_t, int, int, int, cudaStream_t);
 bool esmm_tc_supported(const void*, int64_t, const void*, int64_t, int64_t, const void*, int64_t, const void*, int64_t,
                        const float*, int64_t, int64_t, int);
 int esmm_tc_launch(const void*, int64_t, const void*, int, int64_t, int64_t, const float*, int64_t, void*, int64_t, void*,
                    int64_t, const int32_t*, const int32_t*, const int32_t*, const int32_t*, int, int64_t, int64_t, int64_t, int,
                    int, int, cudaStream_t);
-bool estmm_tc_supported(const void*, int64_t, const void*, int64_t, const void*, int64_t, int64_t, int64_t, int, int);
+bool estmm_tc_supported(const void*, int64_t, const void*, int64_t, const void*, int64_t, int64_t, int64_t, int64_t, int, int);
 int estmm_tc_launch(const void*, int64_t, const void*, int64_t, const int32_t*, int, int64_t, int64_t, int64_t, void*, int64_t,
-                    int64_t, int, int, int, cudaStream_t);
+                    int64_t, int64_t, int64_t, int, int, int, cudaStream_t);
 }  // namespace hexa
 
 using namespace hexa;
@@ -49,23 +49,38 @@ extern "C" int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout
 }
 
 extern "C" int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets, int E,
-                          int64_t row_cap, int64_t m, int64_t n, void* out, int64_t ldo, int64_t o_estride, int dtype,
-                          int out_dtype, int beta, int engine, void* stream_) {
+                          int64_t row_cap, int64_t m, int64_t n, void* out, int64_t ldo, int64_t o_estride, int64_t m_split,
+                          int64_t split_stride, int dtype, int out_dtype, int beta, int engine, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   HEXA_REQUIRE(p && q && out && pad_offsets, "hexa_estmm: null pointer");
   HEXA_REQUIRE(E > 0 && row_cap >= 0 && row_cap % kRowTile == 0 && m > 0 && n > 0,
                "hexa_estmm: bad sizes (row_capacity must be a multiple of %d)", kRowTile);
-  HEXA_REQUIRE(ldp >= m && ldq >= n && ldo >= n && o_estride >= (m - 1) * ldo + n, "hexa_estmm: leading dimension too small");
+  if (m_split <= 0 || m_split >= m) { m_split = m; split_stride = 0; }   // plain [E, m, n] output
+  HEXA_REQUIRE(ldp >= m && ldq >= n && ldo >= n && o_estride >= (m_split - 1) * ldo + n, "hexa_estmm: leading dimension too small");
+  HEXA_REQUIRE(split_stride >= 0, "hexa_estmm: negative split_stride");
   HEXA_REQUIRE(dtype == HEXA_F32 || dtype == HEXA_F16 || dtype == HEXA_BF16, "hexa_estmm: bad dtype %d", dtype);
   HEXA_REQUIRE(out_dtype == HEXA_F32 || out_dtype == dtype, "hexa_estmm: out_dtype must be fp32 or the input dtype");
   HEXA_REQUIRE(beta == 0 || beta == 1, "hexa_estmm: beta must be 0 or 1");
   HEXA_REQUIRE(engine >= HEXA_ENGINE_AUTO && engine <= HEXA_ENGINE_SIMT, "hexa_estmm: bad engine %d", engine);
-  const bool tc_ok = estmm_tc_supported(p, ldp, q, ldq, out, ldo, o_estride, n, dtype, out_dtype);
+  const bool tc_ok = estmm_tc_supported(p, ldp, q, ldq, out, ldo, o_estride, split_stride, n, dtype, out_dtype);
   if (engine == HEXA_ENGINE_TCGEN05 && !tc_ok) {
     set_error("hexa_estmm: tcgen05 engine needs 16-bit inputs, 16-byte aligned pointers and leading dimensions / n that are multiples of 8");
     return HEXA_ERR_UNSUPPORTED;
   }
   if (engine != HEXA_ENGINE_SIMT && tc_ok)
-    return estmm_tc_launch(p, ldp, q, ldq, pad_offsets, E, row_cap, m, n, out, ldo, o_estride, dtype, out_dtype, beta, stream);
-  return estmm_simt_launch(p, ldp, q, ldq, pad_offsets, E, m, n, out, ldo, o_estride, dtype, out_dtype, beta, stream);
+    return estmm_tc_launch(p, ldp, q, ldq, pad_offsets, E, row_cap, m, n, out, ldo, o_estride, m_split, split_stride, dtype, out_dtype,
+                           beta, stream);
+  return estmm_simt_launch(p, ldp, q, ldq, pad_offsets, E, m, n, out, ldo, o_estride, m_split, split_stride, dtype, out_dtype, beta,
+                           stream);
+}
+
+extern "C" int hexa_copy_2d(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes, int64_t width_bytes,
+                            int64_t height, void* stream_) {
+  HEXA_REQUIRE(dst && src, "hexa_copy_2d: null pointer");
+  HEXA_REQUIRE(width_bytes >= 0 && height >= 0 && dst_pitch_bytes >= width_bytes && src_pitch_bytes >= width_bytes,
+               "hexa_copy_2d: bad sizes");
+  if (width_bytes == 0 || height == 0) return HEXA_OK;
+  HEXA_CUDA(cudaMemcpy2DAsync(dst, (size_t)dst_pitch_bytes, src, (size_t)src_pitch_bytes, (size_t)width_bytes, (size_t)height,
+                              cudaMemcpyDeviceToDevice, (cudaStream_t)stream_));
+  return HEXA_OK;
 }

@@ -191,6 +191,9 @@ void set_error(const char* fmt, ...) {
 }
 int32_t* status_word() { return g_status; }
 
+static int g_sm_limit = 0;
+int sm_limit() { return g_sm_limit; }
+
 int sm_count() {
   static int cached[64];
   int dev = 0;
@@ -208,6 +211,10 @@ int sm_count() {
 using namespace hexa;
 
 extern "C" int hexa_version(void) { return 100; }
+extern "C" int hexa_set_sm_limit(int n) {
+  hexa::g_sm_limit = n > 0 ? n : 0;
+  return HEXA_OK;
+}
 extern "C" const char* hexa_last_error_string(void) { return hexa::g_err; }
 extern "C" int hexa_set_status_word(int32_t* status) {
   hexa::g_status = status;

@@ -54,27 +54,41 @@ def all_reduce_avg(t: Tensor, group) -> Tensor:
     return t
 
 
-def reduce_scatter_hidden_avg(full: Tensor, split: List[int], rank: int, group) -> Tensor:
-    """Mean over ranks of `full` [E, H, ...], returning this rank's hidden slice [E, split[rank], ...].
+def reduce_scatter_packed_avg(packed: Tensor, group, out: Optional[Tensor] = None) -> Tensor:
+    """Mean over ranks of a gradient that is already laid out [W, E, loc, ...]: one reduce_scatter_tensor, no copies."""
+    if out is None:
+        out = packed.new_empty(tuple(packed.shape[1:]))
+    dist.reduce_scatter_tensor(out, packed, op=dist.ReduceOp.AVG, group=group)
+    return out
 
-    NCCL: one reduce_scatter_tensor over slices padded to the largest one.  gloo: all-reduce + slice."""
+
+def reduce_scatter_hidden_avg(full: Tensor, split: List[int], rank: int, group) -> Tensor:
+    """Mean over ranks of `full` [E, H, ...], returning this rank's hidden slice padded to the widest slice:
+    [E, max(split), ...] with zeros behind the first split[rank] hidden units (the shape parameters are stored in).
+
+    NCCL: one reduce_scatter_tensor over the padded slices.  gloo: all-reduce + slice."""
     W = len(split)
-    lo = sum(split[:rank])
+    lo, n, bound = sum(split[:rank]), split[rank], max(split)
+    E = full.shape[0]
+    tail = tuple(full.shape[2:])
     if W == 1:
         return full
     if not _is_nccl(group):
         red = all_reduce_avg(full.contiguous(), group)
-        return red[:, lo: lo + split[rank]]
-    bound = max(split)
-    E = full.shape[0]
-    packed = full.new_zeros((W, E, bound) + tuple(full.shape[2:]))
+        out = full.new_zeros((E, bound) + tail)
+        out[:, :n].copy_(red[:, lo: lo + n])
+        return out
+    even = all(s_ == bound for s_ in split)
+    packed = full.new_empty((W, E, bound) + tail)
     off = 0
-    for r, n in enumerate(split):
-        packed[r, :, :n].copy_(full[:, off: off + n])
-        off += n
-    out = full.new_empty((E, bound) + tuple(full.shape[2:]))
+    for r, nr in enumerate(split):
+        packed[r, :, :nr].copy_(full[:, off: off + nr])
+        if nr < bound:
+            packed[r, :, nr:].zero_()
+        off += nr
+    out = full.new_empty((E, bound) + tail)
     dist.reduce_scatter_tensor(out, packed, op=dist.ReduceOp.AVG, group=group)
-    return out[:, : split[rank]]
+    return out
 
 
 def all_gather_tokens(t: Tensor, sizes: List[int], group) -> Tensor:
@@ -137,6 +151,10 @@ def simplified_extract_critical(scores, top_k, loss_fn=losses.gshard_loss):
 def _stack_ids(indices_: List[Tensor], device) -> Tensor:
     """k int vectors [T] -> one int32 [k, T] tensor (route-major, what the routing kernel reads)."""
     return torch.stack([i.reshape(-1).to(device=device, dtype=torch.int32) for i in indices_], dim=0).contiguous()
+
+
+def x_is_cuda(t: Tensor) -> bool:
+    return t.is_cuda
 
 
 def _cast(w: Optional[Tensor], dtype) -> Optional[Tensor]:
@@ -215,16 +233,26 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
         if cfg.data_centric:
             if W > 1:
                 # full expert weights of this layer from the pipeline-shared cache; start fetching the next layer's
-                cfg.cache.prefetch(stage + 1)
-                w1, w2, b1 = cfg.cache.get(stage)
+                # fc1 can start as soon as its weights are in; fc2's may still be arriving
+                w1, w2, b1 = cfg.cache.get(stage, wait=("w1", "b1"))
+                cfg.cache.prefetch(stage + 1)                     # overlaps this layer's kernels
+                cfg.cache.limit_compute_sms(cfg.cache.uses_sms() and stage + 1 < cfg.cache.o.total_depth_moe)
+                before_fc2 = lambda: cfg.cache.wait(stage, "w2")
             else:
                 w1, w2, b1 = fc1_w, fc2_w, fc1_bias
-            w1, w2 = _cast(w1.detach(), dtype), _cast(w2.detach(), dtype)
-            y, st = cfg.backend.moe_forward(x, ids, w1, w2, None if b1 is None else b1.detach(),
+                before_fc2 = None
+            if w1.dtype != dtype or w2.dtype != dtype:            # a cast reads both tensors now
+                if before_fc2 is not None:
+                    before_fc2()
+                    before_fc2 = None
+                w1, w2 = _cast(w1.detach(), dtype), _cast(w2.detach(), dtype)
+            y, st = cfg.backend.moe_forward(x, ids, w1.detach(), w2.detach(), None if b1 is None else b1.detach(),
                                             None if fc2_bias is None else fc2_bias.detach(), cfg.act_id,
-                                            act_fn=cfg.activation_fn, route_major=True, need_state=need_state)
+                                            act_fn=cfg.activation_fn, route_major=True, need_state=need_state,
+                                            before_fc2=before_fc2)
             if W > 1:
                 cfg.cache.release(stage)
+                cfg.cache.limit_compute_sms(False)
             ctx.sizes = None
             ctx.local_w = (w1, w2) if W == 1 else None
         else:
@@ -258,21 +286,25 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
 
         if cfg.data_centric:
             if W > 1:
-                cfg.cache.prefetch(stage - 1)
-                w1, w2, _ = cfg.cache.get(stage)
+                w1, w2, _ = cfg.cache.get(stage, order=("w2", "w1"), wait=("w2", "w1"))
+                cfg.cache.prefetch(stage - 1, order=("w2", "w1"))
                 w1, w2 = _cast(w1.detach(), dtype), _cast(w2.detach(), dtype)
             else:
                 w1, w2 = ctx.local_w
             split = [cfg.local_dim_list_all[r][stage] for r in range(W)]
-            dh, dw2, db2 = be.moe_backward_fc2(st, dy, w2, cfg.act_id, has_b2=ctx.has_b2, grad_dtype=w2_dt)
-            pending = cfg.cache.reduce_async(dw2, db2, split, rank) if W > 1 else None   # overlaps the fc1 backward
-            dx, dw1, db1 = be.moe_backward_fc1(st, dh, w1, has_b1=ctx.has_b1, grad_dtype=w1_dt)
+            # with equal slices on NCCL the weight gradients are produced directly in the [W, E, loc, d] layout the
+            # reduce-scatter reads (no packing pass)
+            packed = W > 1 and x_is_cuda(dy) and _is_nccl(cfg.group) and all(s_ == split[0] for s_ in split)
+            kw = dict(ranks=W) if packed else {}
+            dh, dw2, db2 = be.moe_backward_fc2(st, dy, w2, cfg.act_id, has_b2=ctx.has_b2, grad_dtype=w2_dt, **kw)
+            if W > 1:   # reductions run on the side stream; the results are handed to the parameters when backward ends
+                cfg.cache.reduce_deferred(stage, "fc2", dw2, None if db2 is None else db2.to(b2_dt), split, rank, packed)
+                cfg.cache.limit_compute_sms(True)
+            dx, dw1, db1 = be.moe_backward_fc1(st, dh, w1, has_b1=ctx.has_b1, grad_dtype=w1_dt, **kw)
             if W > 1:
                 cfg.cache.release(stage)
-                dw2, db2 = pending.wait()
-                dw1 = reduce_scatter_hidden_avg(dw1, split, rank, cfg.group)
-                if db1 is not None:
-                    db1 = reduce_scatter_hidden_avg(db1, split, rank, cfg.group)
+                cfg.cache.reduce_deferred(stage, "fc1", dw1, None if db1 is None else db1.to(b1_dt), split, rank, packed)
+                dw1 = dw2 = db1 = db2 = None
         else:
             sizes = ctx.sizes
             w1, w2 = ctx.local_w

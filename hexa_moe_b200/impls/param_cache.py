@@ -16,6 +16,7 @@ with events, so no host thread ever blocks.
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
@@ -24,24 +25,16 @@ import torch.distributed as dist
 from . import layers as _layers
 
 
-class _Pending:
-    """Result of reduce_async: the reduced slices, valid after wait()."""
-
-    def __init__(self, event, tensors):
-        self._event, self._tensors = event, tensors
-
-    def wait(self):
-        if self._event is not None:
-            torch.cuda.current_stream().wait_event(self._event)
-        return self._tensors
-
-
 class PipelineSharedCache:
     def __init__(self, owner):
         self.o = owner            # the MoE_Cascaded module (parameters, split tables, group)
         self.slots = None         # two dicts: w1, w2, b1 flat storage + bookkeeping
         self.stage_buf = None
+        self._peers = None
+        self._p2p = False
         self.side: Optional[torch.cuda.Stream] = None
+        self._pending = []
+        self._callback_queued = False
 
     # -- storage ---------------------------------------------------------------------------------
     def _ensure(self, device, dtype):
@@ -51,14 +44,14 @@ class PipelineSharedCache:
         E = o.num_global_experts
         n1 = E * o.hidden_size_bound * o.input_dim_bound
         n2 = E * o.hidden_size_bound * o.output_dim_bound
-        W = o.world_size
-        s1 = W * E * max(o.local_dim_bound_list) * o.input_dim_bound
-        s2 = W * E * max(o.local_dim_bound_list) * o.output_dim_bound
         mk = lambda n: torch.empty(n, device=device, dtype=dtype)
         self.slots = [dict(w1=mk(n1), w2=mk(n2), b1=mk(E * o.hidden_size_bound) if o.has_fc1_bias else None,
-                           stage=-1, ready=None, free=None) for _ in range(2)]
-        self.stage_buf = dict(w1=mk(s1), w2=mk(s2), b1=mk(W * E * max(o.local_dim_bound_list)) if o.has_fc1_bias else None)
+                           stage=-1, ready={}, free=None) for _ in range(2)]
+        self.stage_buf = None      # staging for the NCCL path, allocated on first use
         self.side = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+        self._peers = None
+        self._peer_ptrs = None
+        self._p2p = device.type == "cuda" and os.environ.get("HEXA_P2P_GATHER", "1") != "0"
 
     def invalidate(self):
         """Forget cached weights (call when parameters may have changed, i.e. at the first MoE layer of a step)."""
@@ -74,59 +67,159 @@ class PipelineSharedCache:
         w1 = slot["w1"][: E * H * d_in].view(E, H, d_in)
         w2 = slot["w2"][: E * H * d_out].view(E, H, d_out)
         b1 = slot["b1"][: E * H].view(E, H) if slot["b1"] is not None else None
-        return w1, w2, b1
+        return dict(w1=w1, w2=w2, b1=b1)
 
-    def _gather_into(self, slot, stage):
+    def _local(self, stage):
+        o = self.o
+        return dict(w1=o.batched_fc1_w[stage].data, w2=o.batched_fc2_w[stage].data,
+                    b1=o.batched_fc1_bias[stage].data if o.has_fc1_bias else None)
+
+    def _peer_setup(self):
+        """Map every rank's parameter slices into this process (CUDA IPC over NVLink peer memory) so that a gather
+        is a handful of copy-engine transfers straight into the [E, H, d] slot: no SMs, no staging, no unpack pass.
+        Returns False (and the cache falls back to NCCL all-gathers) if the mapping cannot be made."""
+        o = self.o
+        ptrs = tuple(t.data_ptr() for st in range(o.total_depth_moe) for t in self._local(st).values() if t is not None)
+        if self._peers is not None and self._peer_ptrs == ptrs:
+            return True
+        try:
+            from torch.multiprocessing.reductions import rebuild_cuda_tensor, reduce_tensor
+            mine = [{k: (None if t is None else reduce_tensor(t)[1]) for k, t in self._local(st).items()}
+                    for st in range(o.total_depth_moe)]
+            everyone = [None] * o.world_size
+            dist.all_gather_object(everyone, mine, group=o.group)
+            peers = []
+            for r, handles in enumerate(everyone):
+                if r == o.local_rank:
+                    peers.append([self._local(st) for st in range(o.total_depth_moe)])
+                else:
+                    peers.append([{k: (None if a is None else rebuild_cuda_tensor(*a)) for k, a in h.items()} for h in handles])
+            # one framework copy from every peer device turns on direct peer access for this process; without it
+            # the driver stages cross-device copies through host memory (26 GB/s instead of ~770 GB/s)
+            probe = torch.empty(1, device=self.side.device, dtype=peers[o.local_rank][0]["w1"].dtype)
+            for r in range(o.world_size):
+                if r != o.local_rank:
+                    probe.copy_(peers[r][0]["w1"].view(-1)[:1])
+            ok = torch.tensor([1], device=self.side.device)
+        except Exception:  # noqa: BLE001  (no IPC between these processes: different nodes, masked devices, ...)
+            peers, ok = None, torch.tensor([0], device=self.side.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=o.group)       # all ranks take the same path
+        if int(ok.item()) == 0:
+            self._p2p = False
+            self._peers = None
+            return False
+        self._peers, self._peer_ptrs = peers, ptrs
+        return True
+
+    def _gather_peer(self, slot, stage, order):
+        """Copy-engine gather: for every tensor and every rank, E blocks of loc_r * d elements from the owner's
+        parameter storage into this rank's slot."""
+        from .. import ops as _ops
+        o = self.o
+        W, E = o.world_size, o.num_global_experts
+        split = [o.local_dim_list_all[r][stage] for r in range(W)]
+        views = self._views(slot, stage)
+        if stage == 0 or self._sync_needed:
+            # every rank's parameters are final (its optimizer has run) before anyone reads them
+            dist.all_reduce(self._flag, group=o.group)
+            self._sync_needed = False
+        for kind in order:
+            full = views[kind]
+            if full is None:
+                continue
+            inner = full.shape[2] if full.dim() == 3 else 1
+            off = 0
+            for r in range(W):
+                rr = (o.local_rank + 1 + r) % W                 # start with the neighbour: spreads the load over the links
+                src = self._peers[rr][stage][kind]
+                nloc = split[rr]
+                lo = sum(split[:rr])
+                _ops.copy_2d(full[:, lo: lo + nloc], full.stride(0), src, src.stride(0), nloc * inner, E)
+            ev = torch.cuda.Event()
+            ev.record(self.side)
+            slot["ready"][kind] = ev
+
+    def _gather_nccl(self, slot, stage, order):
         o = self.o
         W, E = o.world_size, o.num_global_experts
         bound = o.local_dim_bound_list[stage]
         split = [o.local_dim_list_all[r][stage] for r in range(W)]
-        w1, w2, b1 = self._views(slot, stage)
-        jobs = [(o.batched_fc1_w[stage].data, self.stage_buf["w1"], w1), (o.batched_fc2_w[stage].data, self.stage_buf["w2"], w2)]
-        if o.has_fc1_bias:
-            jobs.append((o.batched_fc1_bias[stage].data, self.stage_buf["b1"], b1))
-        for local, staging, full in jobs:
-            tail = tuple(local.shape[2:])
-            n = W * E * bound * (tail[0] if tail else 1)
-            st = staging[:n].view((W, E, bound) + tail)
-            dist.all_gather_into_tensor(st.view((W * E, bound) + tail), local.contiguous(), group=o.group)
+        views, local = self._views(slot, stage), self._local(stage)
+        if self.stage_buf is None:
+            n = W * E * max(o.local_dim_bound_list) * max(o.input_dim_bound, o.output_dim_bound)
+            self.stage_buf = torch.empty(n, device=local["w1"].device, dtype=local["w1"].dtype)
+        for kind in order:
+            full = views[kind]
+            if full is None:
+                continue
+            tail = tuple(local[kind].shape[2:])
+            inner = tail[0] if tail else 1
+            st = self.stage_buf[: W * E * bound * inner].view((W, E, bound) + tail)
+            dist.all_gather_into_tensor(st.view((W * E, bound) + tail), local[kind].contiguous(), group=o.group)
             off = 0
-            for r, nloc in enumerate(split):                      # unpack: one strided copy per rank
-                full[:, off: off + nloc].copy_(st[r, :, :nloc])
+            for r, nloc in enumerate(split):                      # unpack: E blocks of nloc*inner elements per rank
+                if st.is_cuda:                                    # block copy (cudaMemcpy2DAsync): no SMs spent on it
+                    from .. import ops as _ops
+                    _ops.copy_2d(full[:, off: off + nloc], full.stride(0), st[r], st.stride(1), nloc * inner, E)
+                else:
+                    full[:, off: off + nloc].copy_(st[r, :, :nloc])
                 off += nloc
+            if self.side is not None:
+                ev = torch.cuda.Event()
+                ev.record(self.side)
+                slot["ready"][kind] = ev
 
-    def prefetch(self, stage: int):
-        """Start assembling layer `stage` (no-op when out of range or already present)."""
+    def prefetch(self, stage: int, order=("w1", "b1", "w2")):
+        """Start assembling layer `stage` (no-op when out of range or already present).  `order`: which tensors,
+        first needed first (forward: fc1 then fc2; backward: ("w2", "w1"))."""
         o = self.o
         if stage < 0 or stage >= o.total_depth_moe or o.world_size == 1:
             return
         p = o.batched_fc1_w[stage]
         self._ensure(p.device, p.dtype)
         slot = self.slots[stage % 2]
-        if slot["stage"] == stage:
+        if slot["stage"] == stage and all(k in slot["ready"] or self.side is None for k in order if self._views(slot, stage)[k] is not None):
             return
+        if slot["stage"] != stage:
+            slot["ready"] = {}
+        todo = tuple(k for k in order if k not in slot["ready"])
         if self.side is None:                                    # CPU / gloo: synchronous
-            self._gather_into(slot, stage)
+            self._gather_nccl(slot, stage, todo)
+            for k in todo:
+                slot["ready"][k] = None
         else:
+            use_peer = self._p2p and self._peer_setup()
+            if not hasattr(self, "_flag"):
+                self._flag = torch.zeros(1, device=self.side.device)
+                self._sync_needed = True
             cur = torch.cuda.current_stream()
             if slot["free"] is not None:
                 self.side.wait_event(slot["free"])               # the slot's previous reader has finished
             if stage == 0 or slot["free"] is None:
                 self.side.wait_stream(cur)                       # parameters may have just been updated
             with torch.cuda.stream(self.side):
-                self._gather_into(slot, stage)
-                ev = torch.cuda.Event()
-                ev.record(self.side)
-            slot["ready"] = ev
+                if use_peer:
+                    self._gather_peer(slot, stage, todo)
+                else:
+                    self._gather_nccl(slot, stage, todo)
         slot["stage"] = stage
 
-    def get(self, stage: int):
-        """Full (w1 [E,H,d_in], w2 [E,H,d_out], b1 [E,H] | None) of layer `stage`; orders the current stream after the gather."""
-        self.prefetch(stage)
+    def wait(self, stage: int, kind: str):
+        """Order the current stream after the arrival of one tensor ("w1", "w2" or "b1") of layer `stage`."""
         slot = self.slots[stage % 2]
-        if slot["ready"] is not None:
-            torch.cuda.current_stream().wait_event(slot["ready"])
-        return self._views(slot, stage)
+        ev = slot["ready"].get(kind)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def get(self, stage: int, order=("w1", "b1", "w2"), wait=("w1", "b1", "w2")):
+        """Full (w1 [E,H,d_in], w2 [E,H,d_out], b1 [E,H] | None) of layer `stage`.  Starts the gather if needed and
+        orders the current stream after the tensors named in `wait`; call wait() for the others before using them."""
+        self.prefetch(stage, order)
+        v = self._views(self.slots[stage % 2], stage)
+        for k in wait:
+            if v[k] is not None:
+                self.wait(stage, k)
+        return v["w1"], v["w2"], v["b1"]
 
     def release(self, stage: int):
         """The current stream is done reading layer `stage` (everything enqueued so far)."""
@@ -137,24 +230,77 @@ class PipelineSharedCache:
         self.slots[stage % 2]["free"] = ev
 
     # -- gradient reduction ----------------------------------------------------------------------
-    def reduce_async(self, dw2, db2, split: List[int], rank: int) -> _Pending:
-        """Reduce-scatter(AVG) dw2 along the hidden dimension and all-reduce(AVG) db2 on the side stream,
-        so the transfer overlaps the fc1 half of the backward."""
+    def reduce_deferred(self, stage: int, which: str, dw, db, split: List[int], rank: int, packed: bool = False):
+        """Average one layer's expert gradients over the ranks without stalling the compute stream.
+
+        dw [E, H, d*] (and db: [E, H] for "fc1", [E, d_out] for "fc2") are reduce-scattered along the hidden
+        dimension (fc2's bias: all-reduced) on the side stream.  The reduced slices are not returned through
+        autograd: they are accumulated into the parameters' .grad by a callback that the autograd engine runs
+        when the whole backward pass has finished, so the transfer overlaps everything that is still to run."""
         o = self.o
+        if which == "fc1":
+            targets = [(o.batched_fc1_w[stage], dw, True), (o.batched_fc1_bias[stage] if o.has_fc1_bias else None, db, True)]
+        else:
+            targets = [(o.batched_fc2_w[stage], dw, True), (o.batched_fc2_bias[stage] if o.has_fc2_bias else None, db, False)]
+        targets = [t for t in targets if t[0] is not None and t[1] is not None]
+
+        def run():
+            outs = []
+            for prm, g, sharded in targets:
+                if sharded and packed and g.dim() == prm.dim() + 1:     # already [W, E, loc, d]
+                    outs.append((prm, _layers.reduce_scatter_packed_avg(g, o.group)))
+                elif sharded:
+                    outs.append((prm, _layers.reduce_scatter_hidden_avg(g, split, rank, o.group)))
+                else:
+                    outs.append((prm, _layers.all_reduce_avg(g, o.group)))
+            return outs
+
         if self.side is None:
-            out = _layers.reduce_scatter_hidden_avg(dw2, split, rank, o.group)
-            if db2 is not None:
-                _layers.all_reduce_avg(db2, o.group)
-            return _Pending(None, (out, db2))
-        cur = torch.cuda.current_stream()
-        self.side.wait_stream(cur)
-        with torch.cuda.stream(self.side):
-            out = _layers.reduce_scatter_hidden_avg(dw2, split, rank, o.group)
-            if db2 is not None:
-                _layers.all_reduce_avg(db2, o.group)
-            ev = torch.cuda.Event()
-            ev.record(self.side)
-        for t in (dw2, db2, out):
-            if t is not None:
-                t.record_stream(self.side)
-        return _Pending(ev, (out, db2))
+            self._pending.append((None, run(), None))
+        else:
+            cur = torch.cuda.current_stream()
+            self.side.wait_stream(cur)
+            with torch.cuda.stream(self.side):
+                outs = run()
+                ev = torch.cuda.Event()
+                ev.record(self.side)
+            # the inputs stay referenced until the flush (after the compute stream has waited for `ev`), so their
+            # memory cannot be handed out again while the side stream still reads it
+            self._pending.append((ev, outs, [g for _, g, _ in targets]))
+        if not self._callback_queued:
+            self._callback_queued = True
+            torch.autograd.Variable._execution_engine.queue_callback(self._flush_grads)
+
+    def _flush_grads(self):
+        """End of a backward pass: wait for the reductions and add their results to the parameters' .grad."""
+        self._callback_queued = False
+        pending, self._pending = self._pending, []
+        for ev, outs, _keep in pending:
+            if ev is not None:
+                torch.cuda.current_stream().wait_event(ev)
+            for prm, g in outs:
+                if g.shape != prm.shape:        # a slice narrower than the stored (padded) parameter
+                    full = torch.zeros_like(prm)
+                    full[:, : g.shape[1]].copy_(g)
+                    g = full
+                if prm.grad is None:
+                    prm.grad = g
+                else:
+                    prm.grad.add_(g)
+        self.limit_compute_sms(False)
+
+    def uses_sms(self) -> bool:
+        """True when gathers run as NCCL kernels (the peer-copy path leaves every SM to the GEMMs)."""
+        return not (self._p2p and self._peers is not None)
+
+    def limit_compute_sms(self, on: bool):
+        """While a collective may be running, keep the persistent GEMM kernels off `HEXA_COMM_SMS` SMs (default 16)
+        so that NCCL's CTAs and the GEMM's static tile schedule do not wait for each other."""
+        if self.side is None:
+            return
+        from .. import _lib
+        n = 0
+        if on:
+            reserve = int(os.environ.get("HEXA_COMM_SMS", "16"))
+            n = max(2, torch.cuda.get_device_properties(self.side.device).multi_processor_count - reserve) if reserve > 0 else 0
+        _lib.lib().hexa_set_sm_limit(n)

@@ -154,24 +154,40 @@ def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Opti
 
 
 def estmm(p: torch.Tensor, q: torch.Tensor, r: Routing, out_dtype: Optional[torch.dtype] = None,
-          out: Optional[torch.Tensor] = None, beta: int = 0, engine: int = L.ENGINE_AUTO) -> torch.Tensor:
-    """out[e] = p_e^T q_e over expert e's rows: [E, p.cols, q.cols]."""
+          out: Optional[torch.Tensor] = None, beta: int = 0, engine: int = L.ENGINE_AUTO, ranks: int = 1) -> torch.Tensor:
+    """out[e] = p_e^T q_e over expert e's rows: [E, p.cols, q.cols].
+    ranks > 1 (p.cols divisible by it): the result is laid out [ranks, E, p.cols/ranks, q.cols], i.e. already
+    grouped by the rank that owns each slice of the hidden dimension (what a reduce-scatter consumes)."""
     if r.align % L.ROW_TILE:
         raise L.HexaError("estmm: routing must be aligned to 128 rows")
     m, n = p.shape[1], q.shape[1]
     if p.dtype != q.dtype:
         raise L.HexaError("estmm: p and q dtypes differ")
-    if out is None:
-        out_dtype = out_dtype or p.dtype
-        out = torch.empty(r.num_experts, m, n, dtype=out_dtype, device=p.device)
-        if beta:
-            raise L.HexaError("estmm: beta=1 needs an existing out")
-    if out.stride(2) != 1:
+    if ranks > 1:
+        if m % ranks:
+            raise L.HexaError("estmm: the row count must be divisible by ranks")
+        if out is None:
+            out = torch.empty(ranks, r.num_experts, m // ranks, n, dtype=out_dtype or p.dtype, device=p.device)
+        ldo, estride, m_split, split_stride = out.stride(2), out.stride(1), m // ranks, out.stride(0)
+    else:
+        if out is None:
+            if beta:
+                raise L.HexaError("estmm: beta=1 needs an existing out")
+            out = torch.empty(r.num_experts, m, n, dtype=out_dtype or p.dtype, device=p.device)
+        ldo, estride, m_split, split_stride = out.stride(1), out.stride(0), 0, 0
+    if out.stride(-1) != 1:
         raise L.HexaError("estmm: out must have unit inner stride")
     with _Timed("estmm", 2.0 * r.num_tokens * r.top_k * m * n):
         check(lib().hexa_estmm(ptr(p), _ld(p), ptr(q), _ld(q), ptr(r.pad_offsets), r.num_experts, r.row_capacity, m, n, ptr(out),
-                               out.stride(1), out.stride(0), dt(p), dt(out), beta, engine, stream_of(p)), "hexa_estmm")
+                               ldo, estride, m_split, split_stride, dt(p), dt(out), beta, engine, stream_of(p)), "hexa_estmm")
     return out
+
+
+def copy_2d(dst: torch.Tensor, dst_pitch: int, src: torch.Tensor, src_pitch: int, width: int, height: int):
+    """Device-to-device copy of `height` blocks of `width` elements (pitches in elements) on the current stream of
+    dst's device; src may live on another GPU (peer memory)."""
+    es = src.element_size()
+    check(lib().hexa_copy_2d(ptr(dst), dst_pitch * es, ptr(src), src_pitch * es, width * es, height, stream_of(dst)), "hexa_copy_2d")
 
 
 def ess(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -214,9 +230,10 @@ def _f32(t):
 
 
 def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=False, engine=L.ENGINE_AUTO,
-                need_state=True):
+                need_state=True, before_fc2=None):
     """y[t] = sum_j fc2(act(fc1(x[t]; e_j)); e_j).  x [T,d]; ids int32 [T,k] ([k,T] if route_major);
-    w1 [E,H,d]; w2 [E,H,d_out]; b1 [E,H] / b2 [E,d_out] or None.
+    w1 [E,H,d]; w2 [E,H,d_out]; b1 [E,H] / b2 [E,d_out] or None.  before_fc2: optional callable run on the host
+    between the launches of fc1 and fc2 (the caller may enqueue a stream wait for w2 there).
     act_id: an _lib.ACT_* id fused into the fc1 epilogue, or -1 to call `act_fn` (any elementwise
     callable) between the two ESMMs.  Returns (y [T,d_out], LayerState)."""
     E = w1.shape[0]
@@ -239,18 +256,20 @@ def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=Fa
         else:
             h = act_fn(y1).contiguous()
         mask_pad_rows(h, r)
+    if before_fc2 is not None:      # e.g. wait for w2 to finish arriving from the other ranks
+        before_fc2()
     ys = esmm(h, w2, L.B_KN, r, b2f, L.EPI_LINEAR, engine=engine)
     y = combine_rows(ys, r)
     return y, (LayerState(r, xs, y1, h, g) if need_state else None)
 
 
-def moe_backward_fc2(st: LayerState, dy, w2, act_id: int, has_b2=True, grad_dtype=None, engine=L.ENGINE_AUTO):
+def moe_backward_fc2(st: LayerState, dy, w2, act_id: int, has_b2=True, grad_dtype=None, engine=L.ENGINE_AUTO, ranks=1):
     """First half of the layer backward: (dh [cap,H] = dy W2^T * act'(y1), dw2 [E,H,d_out], db2 [E,d_out] | None).
     Split from the fc1 half so a caller can start reducing dw2/db2 across ranks while fc1 runs."""
     r = st.routing
     dys = gather_rows(dy.contiguous(), r)
     db2 = ess(dys, r) if has_b2 else None
-    dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine)
+    dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine, ranks=ranks)
     if act_id >= 0:
         dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_DACT, act_id, aux=st.y1, engine=engine)
     else:
@@ -260,11 +279,11 @@ def moe_backward_fc2(st: LayerState, dy, w2, act_id: int, has_b2=True, grad_dtyp
     return dh, dw2, db2
 
 
-def moe_backward_fc1(st: LayerState, dh, w1, has_b1=True, grad_dtype=None, engine=L.ENGINE_AUTO):
+def moe_backward_fc1(st: LayerState, dh, w1, has_b1=True, grad_dtype=None, engine=L.ENGINE_AUTO, ranks=1):
     """Second half: (dx [T,d], dw1 [E,H,d], db1 [E,H] | None) from dh."""
     r = st.routing
     db1 = ess(dh, r) if has_b1 else None
-    dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine)
+    dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine, ranks=ranks)
     dxs = esmm(dh, w1, L.B_KN, r, None, L.EPI_LINEAR, engine=engine)
     dx = combine_rows(dxs, r)
     return dx, dw1, db1

@@ -81,6 +81,11 @@ const char* hexa_last_error_string(void);
  * host thread); NULL disables reporting (waits stay bounded). */
 int hexa_set_status_word(int32_t* status);
 
+/* Cap on the SMs the persistent GEMM kernels occupy from now on (process-wide; 0 = all SMs).  Their tile
+ * schedule is static, so they should not share SMs with long-running kernels of other streams (collectives):
+ * set a cap while such kernels may be running.  No counterpart in the reference. */
+int hexa_set_sm_limit(int num_sms);
+
 /* ---- routing: replaces launch_count + launch_assign (include/hexa_moe.h:3-22,
  *      kernels/shared_cuda_core.cu:128-182, 285-333) and kernels/basics.py:counter (89-118) ---- */
 
@@ -138,10 +143,23 @@ int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout, int64_t l
  * out[e] (m x n, ld ldo, expert stride o_estride) = beta*out[e] + sum over rows r of expert e of
  * p[r,:m]^T (outer) q[r,:n].  Experts without rows get beta*out[e] (zeros for beta = 0).
  * p [row_capacity, m] (ldp), q [row_capacity, n] (ldq) in `dtype`; out in `out_dtype`
- * (HEXA_F32 or `dtype`); beta is 0 or 1. */
+ * (HEXA_F32 or `dtype`); beta is 0 or 1.
+ * m_split / split_stride: output row i of expert e is written at
+ *   out + e*o_estride + (i / m_split)*split_stride + (i % m_split)*ldo,
+ * which lets the gradient land directly in the [ranks, E, m/ranks, n] layout a reduce-scatter over the
+ * hidden dimension consumes (m_split = m/ranks, split_stride = E*m_split*ldo, o_estride = m_split*ldo).
+ * Pass m_split = 0 for the plain [E, m, n] layout. */
 int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets,
                int num_experts, int64_t row_capacity, int64_t m, int64_t n, void* out, int64_t ldo,
-               int64_t o_estride, int dtype, int out_dtype, int beta, int engine, void* stream);
+               int64_t o_estride, int64_t m_split, int64_t split_stride, int dtype, int out_dtype, int beta,
+               int engine, void* stream);
+
+/* Strided block copy on the stream (cudaMemcpy2DAsync, device to device): `height` rows of `width_bytes`.
+ * Used to move hidden-dimension slices between the gathered [ranks, E, loc, d] staging layout and
+ * [E, H, d] without spending SMs on it.  No counterpart in the reference (it builds the same views with
+ * cat / permute / contiguous copies, impls/layers.py:112-118). */
+int hexa_copy_2d(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes, int64_t width_bytes,
+                 int64_t height, void* stream);
 
 /* ---- ESS: replaces task 2 of launch_fused_grad_bias_*, kernels/fused.py:111-141 ----
  * out[e,:] = sum of src rows of expert e, fp32 [E, cols] (ldo).  Deterministic two-pass

@@ -12,7 +12,9 @@ class _State:
     pass
 
 
-def moe_forward(x, ids, w1, w2, b1, b2, act_id, act_fn=None, route_major=False, engine=0, need_state=True):
+def moe_forward(x, ids, w1, w2, b1, b2, act_id, act_fn=None, route_major=False, engine=0, need_state=True, before_fc2=None):
+    if before_fc2 is not None:
+        before_fc2()
     ids_tk = ids.t().contiguous() if route_major else ids
     st = _State()
     st.x, st.ids, st.w1, st.w2, st.b1, st.b2, st.act = x, ids_tk, w1, w2, b1, b2, act_fn
@@ -28,13 +30,13 @@ def _full(st, dy):
     return st.res
 
 
-def moe_backward_fc2(st, dy, w2, act_id, has_b2=True, grad_dtype=None, engine=0):
+def moe_backward_fc2(st, dy, w2, act_id, has_b2=True, grad_dtype=None, engine=0, ranks=1):
     r = _full(st, dy)
     gd = grad_dtype or dy.dtype
     return None, r["dw2"].to(gd), (r["db2"].float() if has_b2 else None)
 
 
-def moe_backward_fc1(st, dh, w1, has_b1=True, grad_dtype=None, engine=0):
+def moe_backward_fc1(st, dh, w1, has_b1=True, grad_dtype=None, engine=0, ranks=1):
     r = st.res
     gd = grad_dtype or st.x.dtype
     return r["dx"].to(st.x.dtype), r["dw1"].to(gd), (r["db1"].float() if has_b1 else None)

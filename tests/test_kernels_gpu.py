@@ -228,6 +228,24 @@ def _estmm_case(ops, dtype, engine, T, k, E, M, N, out_dtype, seed=0):
     return got
 
 
+@pytest.mark.parametrize("dtype,engine", [(torch.bfloat16, 1), (torch.float32, 2)])
+def test_estmm_rank_grouped_layout_and_copy_2d(ops, dtype, engine):
+    """ranks=W writes the gradient as [W, E, m/W, n] (what a reduce-scatter over the hidden dimension reads);
+    copy_2d moves hidden slices between that layout and [E, m, n]."""
+    T, k, E, M, N, W = 1500, 2, 5, 512, 256, 4
+    ids = make_ids(T, k, E, 8, skew=True)
+    r = ops.route(ids.cuda(), E)
+    p = ops.gather_rows(torch.randn(T, M).to(dtype).cuda(), r); q = ops.gather_rows(torch.randn(T, N).to(dtype).cuda(), r)
+    plain = ops.estmm(p, q, r, out_dtype=torch.float32, engine=engine)
+    grouped = ops.estmm(p, q, r, out_dtype=torch.float32, engine=engine, ranks=W)
+    assert grouped.shape == (W, E, M // W, N)
+    assert torch.equal(grouped.permute(1, 0, 2, 3).reshape(E, M, N), plain)
+    back = torch.empty_like(plain)
+    for w in range(W):
+        ops.copy_2d(back[:, w * (M // W):(w + 1) * (M // W)], back.stride(0), grouped[w], grouped.stride(1), (M // W) * N, E)
+    assert torch.equal(back, plain)
+
+
 def test_estmm_simt_fp32(ops):
     _estmm_case(ops, torch.float32, L().ENGINE_SIMT, T=900, k=2, E=6, M=100, N=72, out_dtype=torch.float32)
 
