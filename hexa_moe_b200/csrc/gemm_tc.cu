@@ -186,6 +186,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
 // bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
 // [46,48) version, [61,64) layout type (2 = SWIZZLE_128B).
@@ -353,14 +364,15 @@ __device__ __forceinline__ void stage_row(uint8_t* buf, int r, const uint32_t (&
     *reinterpret_cast<uint4*>(row + ((c ^ x) << 4)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
 }
 
-// Values of one row chunk for the two possible outputs of the ESMM epilogue: y = acc + bias packed as it is
-// (the saved pre-activation), o = the layer output of this GEMM.  Rows that are padding produce zeros.
+// Values of 16 columns of one row for the two possible outputs of the ESMM epilogue: y = acc + bias packed as it
+// is (the saved pre-activation), o = the layer output of this GEMM.  Rows that are padding produce zeros.  Working on
+// 16 columns at a time keeps few enough values live for the compiler to interleave the independent activations.
 template <int EPI, int ACT>
-__device__ __forceinline__ void epi_values(const float (&f)[32], const uint16_t* xp, bool live, int ncols, int is_bf16,
-                                           uint32_t (&y)[16], uint32_t (&o)[16]) {
+__device__ __forceinline__ void epi_values16(const float (&f)[16], const uint16_t* xp, bool live, int ncols, int is_bf16,
+                                             uint32_t* y, uint32_t* o) {
   if (EPI == HEXA_EPI_DACT) {
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
+    for (int g = 0; g < 2; ++g) {
       // columns at or beyond ncols do not exist (the TMA store clips them): do not read aux there
       const uint4 a = g * 8 < ncols ? *reinterpret_cast<const uint4*>(xp + g * 8) : make_uint4(0, 0, 0, 0);
       const uint32_t* ap = reinterpret_cast<const uint32_t*>(&a);
@@ -372,7 +384,7 @@ __device__ __forceinline__ void epi_values(const float (&f)[32], const uint16_t*
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < 8; ++i) {
       if (EPI == HEXA_EPI_ACT) {
         y[i] = live ? pack2(f[2 * i], f[2 * i + 1], is_bf16) : 0u;
         o[i] = live ? pack2(act_fast<ACT>(f[2 * i]), act_fast<ACT>(f[2 * i + 1]), is_bf16) : 0u;
@@ -566,14 +578,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int cloc = part * (BN / kParts) + cc * 32;
         const int64_t gcol = (int64_t)tile.col0 + cloc;
         if (gcol >= p.n || !tile.valid) break;  // uniform across the four warps of a group
-        uint32_t v[32];
-        if (tile.num_kb > 0) {
-          tmem_ld32(t_row + (uint32_t)cloc, v);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0u;
-        }
         if (MODE == ESTMM) {
+          uint32_t v[32];
+          if (tile.num_kb > 0) {
+            tmem_ld32(t_row + (uint32_t)cloc, v);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
           const int64_t mrow = (int64_t)tile.m0 + rloc;
           if (mrow < p.m) {
             if (p.out_f32) {
@@ -617,33 +629,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         } else {
           const int64_t r = (int64_t)tile.row0 + rloc;
           const bool live = p.row_token == nullptr || p.row_token[r] >= 0;
-          float f[32];
+          uint32_t yv[16], ov[16];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
-          if (p.bias) {
-            const float* bp = p.bias + (int64_t)tile.e * p.ldbias + gcol;
+          for (int hf = 0; hf < 2; ++hf) {
+            const int64_t hcol = gcol + hf * 16;
+            const int ncols = (int)min((int64_t)16, p.n - hcol);   // <= 0: nothing of this half exists
+            uint32_t v[16];
+            tmem_ld16(t_row + (uint32_t)(cloc + hf * 16), v);      // ESMM tiles always have k-blocks
+            float f[16];
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              if (gcol + g * 4 < p.n) {
-                const float4 bv = __ldg(reinterpret_cast<const float4*>(bp + g * 4));
-                f[4 * g] += bv.x; f[4 * g + 1] += bv.y; f[4 * g + 2] += bv.z; f[4 * g + 3] += bv.w;
+            for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
+            if (p.bias && ncols > 0) {
+              const float* bp = p.bias + (int64_t)tile.e * p.ldbias + hcol;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (g * 4 < ncols) {
+                  const float4 bv = __ldg(reinterpret_cast<const float4*>(bp + g * 4));
+                  f[4 * g] += bv.x; f[4 * g + 1] += bv.y; f[4 * g + 2] += bv.z; f[4 * g + 3] += bv.w;
+                }
               }
             }
-          }
-          const uint16_t* xp = p.aux ? reinterpret_cast<const uint16_t*>(p.aux) + r * p.ldaux + gcol : nullptr;
-          uint32_t yv[16], ov[16];
-          const int ncols = (int)min((int64_t)32, p.n - gcol);
-          switch (p.epilogue * 8 + p.act) {
-            case HEXA_EPI_ACT * 8 + HEXA_ACT_RELU: epi_values<HEXA_EPI_ACT, HEXA_ACT_RELU>(f, xp, live, ncols, is_bf16, yv, ov); break;
-            case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU: epi_values<HEXA_EPI_ACT, HEXA_ACT_GELU>(f, xp, live, ncols, is_bf16, yv, ov); break;
-            case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU_TANH: epi_values<HEXA_EPI_ACT, HEXA_ACT_GELU_TANH>(f, xp, live, ncols, is_bf16, yv, ov); break;
-            case HEXA_EPI_ACT * 8 + HEXA_ACT_SILU: epi_values<HEXA_EPI_ACT, HEXA_ACT_SILU>(f, xp, live, ncols, is_bf16, yv, ov); break;
-            case HEXA_EPI_ACT * 8 + HEXA_ACT_NONE: epi_values<HEXA_EPI_ACT, HEXA_ACT_NONE>(f, xp, live, ncols, is_bf16, yv, ov); break;
-            case HEXA_EPI_DACT * 8 + HEXA_ACT_RELU: epi_values<HEXA_EPI_DACT, HEXA_ACT_RELU>(f, xp, live, ncols, is_bf16, yv, ov); break;
-            case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU: epi_values<HEXA_EPI_DACT, HEXA_ACT_GELU>(f, xp, live, ncols, is_bf16, yv, ov); break;
-            case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU_TANH: epi_values<HEXA_EPI_DACT, HEXA_ACT_GELU_TANH>(f, xp, live, ncols, is_bf16, yv, ov); break;
-            case HEXA_EPI_DACT * 8 + HEXA_ACT_SILU: epi_values<HEXA_EPI_DACT, HEXA_ACT_SILU>(f, xp, live, ncols, is_bf16, yv, ov); break;
-            default: epi_values<HEXA_EPI_LINEAR, HEXA_ACT_NONE>(f, xp, live, ncols, is_bf16, yv, ov); break;
+            const uint16_t* xp = p.aux ? reinterpret_cast<const uint16_t*>(p.aux) + r * p.ldaux + hcol : nullptr;
+            uint32_t* yh = yv + hf * 8;
+            uint32_t* oh = ov + hf * 8;
+            switch (p.epilogue * 8 + p.act) {
+              case HEXA_EPI_ACT * 8 + HEXA_ACT_RELU: epi_values16<HEXA_EPI_ACT, HEXA_ACT_RELU>(f, xp, live, ncols, is_bf16, yh, oh); break;
+              case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU: epi_values16<HEXA_EPI_ACT, HEXA_ACT_GELU>(f, xp, live, ncols, is_bf16, yh, oh); break;
+              case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU_TANH: epi_values16<HEXA_EPI_ACT, HEXA_ACT_GELU_TANH>(f, xp, live, ncols, is_bf16, yh, oh); break;
+              case HEXA_EPI_ACT * 8 + HEXA_ACT_SILU: epi_values16<HEXA_EPI_ACT, HEXA_ACT_SILU>(f, xp, live, ncols, is_bf16, yh, oh); break;
+              case HEXA_EPI_ACT * 8 + HEXA_ACT_NONE: epi_values16<HEXA_EPI_ACT, HEXA_ACT_NONE>(f, xp, live, ncols, is_bf16, yh, oh); break;
+              case HEXA_EPI_DACT * 8 + HEXA_ACT_RELU: epi_values16<HEXA_EPI_DACT, HEXA_ACT_RELU>(f, xp, live, ncols, is_bf16, yh, oh); break;
+              case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU: epi_values16<HEXA_EPI_DACT, HEXA_ACT_GELU>(f, xp, live, ncols, is_bf16, yh, oh); break;
+              case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU_TANH: epi_values16<HEXA_EPI_DACT, HEXA_ACT_GELU_TANH>(f, xp, live, ncols, is_bf16, yh, oh); break;
+              case HEXA_EPI_DACT * 8 + HEXA_ACT_SILU: epi_values16<HEXA_EPI_DACT, HEXA_ACT_SILU>(f, xp, live, ncols, is_bf16, yh, oh); break;
+              default: epi_values16<HEXA_EPI_LINEAR, HEXA_ACT_NONE>(f, xp, live, ncols, is_bf16, yh, oh); break;
+            }
           }
           // registers -> swizzled staging tile -> one TMA store per 128x32 block (full 128-byte lines to L2)
           const bool two = (p.epilogue == HEXA_EPI_ACT) && p.aux != nullptr;
