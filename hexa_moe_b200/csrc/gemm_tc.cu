@@ -367,8 +367,8 @@ __device__ __forceinline__ void stage_row(uint8_t* buf, int r, const uint32_t (&
 // Values of 16 columns of one row for the two possible outputs of the ESMM epilogue: y = acc + bias packed as it
 // is (the saved pre-activation), o = the layer output of this GEMM.  Rows that are padding produce zeros.  Working on
 // 16 columns at a time keeps few enough values live for the compiler to interleave the independent activations.
-template <int EPI, int ACT>
-__device__ __forceinline__ void epi_values16(const float (&f)[16], const uint16_t* xp, bool live, int ncols, int is_bf16,
+template <int EPI, int ACT, int is_bf16>
+__device__ __forceinline__ void epi_values16(const float (&f)[16], const uint16_t* xp, bool live, int ncols,
                                              uint32_t* y, uint32_t* o) {
   if (EPI == HEXA_EPI_DACT) {
 #pragma unroll
@@ -652,18 +652,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint16_t* xp = p.aux ? reinterpret_cast<const uint16_t*>(p.aux) + r * p.ldaux + hcol : nullptr;
             uint32_t* yh = yv + hf * 8;
             uint32_t* oh = ov + hf * 8;
+            // one specialisation per (epilogue, activation, 16-bit flavour): no per-element branches
+#define HEXA_EPI_CASE(E_, A_)                                                                          \
+  case E_ * 8 + A_:                                                                                    \
+    if (is_bf16) epi_values16<E_, A_, 1>(f, xp, live, ncols, yh, oh);                                  \
+    else epi_values16<E_, A_, 0>(f, xp, live, ncols, yh, oh);                                          \
+    break;
             switch (p.epilogue * 8 + p.act) {
-              case HEXA_EPI_ACT * 8 + HEXA_ACT_RELU: epi_values16<HEXA_EPI_ACT, HEXA_ACT_RELU>(f, xp, live, ncols, is_bf16, yh, oh); break;
-              case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU: epi_values16<HEXA_EPI_ACT, HEXA_ACT_GELU>(f, xp, live, ncols, is_bf16, yh, oh); break;
-              case HEXA_EPI_ACT * 8 + HEXA_ACT_GELU_TANH: epi_values16<HEXA_EPI_ACT, HEXA_ACT_GELU_TANH>(f, xp, live, ncols, is_bf16, yh, oh); break;
-              case HEXA_EPI_ACT * 8 + HEXA_ACT_SILU: epi_values16<HEXA_EPI_ACT, HEXA_ACT_SILU>(f, xp, live, ncols, is_bf16, yh, oh); break;
-              case HEXA_EPI_ACT * 8 + HEXA_ACT_NONE: epi_values16<HEXA_EPI_ACT, HEXA_ACT_NONE>(f, xp, live, ncols, is_bf16, yh, oh); break;
-              case HEXA_EPI_DACT * 8 + HEXA_ACT_RELU: epi_values16<HEXA_EPI_DACT, HEXA_ACT_RELU>(f, xp, live, ncols, is_bf16, yh, oh); break;
-              case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU: epi_values16<HEXA_EPI_DACT, HEXA_ACT_GELU>(f, xp, live, ncols, is_bf16, yh, oh); break;
-              case HEXA_EPI_DACT * 8 + HEXA_ACT_GELU_TANH: epi_values16<HEXA_EPI_DACT, HEXA_ACT_GELU_TANH>(f, xp, live, ncols, is_bf16, yh, oh); break;
-              case HEXA_EPI_DACT * 8 + HEXA_ACT_SILU: epi_values16<HEXA_EPI_DACT, HEXA_ACT_SILU>(f, xp, live, ncols, is_bf16, yh, oh); break;
-              default: epi_values16<HEXA_EPI_LINEAR, HEXA_ACT_NONE>(f, xp, live, ncols, is_bf16, yh, oh); break;
+              HEXA_EPI_CASE(HEXA_EPI_ACT, HEXA_ACT_RELU)
+              HEXA_EPI_CASE(HEXA_EPI_ACT, HEXA_ACT_GELU)
+              HEXA_EPI_CASE(HEXA_EPI_ACT, HEXA_ACT_GELU_TANH)
+              HEXA_EPI_CASE(HEXA_EPI_ACT, HEXA_ACT_SILU)
+              HEXA_EPI_CASE(HEXA_EPI_ACT, HEXA_ACT_NONE)
+              HEXA_EPI_CASE(HEXA_EPI_DACT, HEXA_ACT_RELU)
+              HEXA_EPI_CASE(HEXA_EPI_DACT, HEXA_ACT_GELU)
+              HEXA_EPI_CASE(HEXA_EPI_DACT, HEXA_ACT_GELU_TANH)
+              HEXA_EPI_CASE(HEXA_EPI_DACT, HEXA_ACT_SILU)
+              default:
+                if (is_bf16) epi_values16<HEXA_EPI_LINEAR, HEXA_ACT_NONE, 1>(f, xp, live, ncols, yh, oh);
+                else epi_values16<HEXA_EPI_LINEAR, HEXA_ACT_NONE, 0>(f, xp, live, ncols, yh, oh);
+                break;
             }
+#undef HEXA_EPI_CASE
           }
           // registers -> swizzled staging tile -> one TMA store per 128x32 block (full 128-byte lines to L2)
           const bool two = (p.epilogue == HEXA_EPI_ACT) && p.aux != nullptr;
