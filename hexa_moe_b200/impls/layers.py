@@ -300,10 +300,12 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
             if W > 1:   # reductions run on the side stream; the results are handed to the parameters when backward ends
                 cfg.cache.reduce_deferred(stage, "fc2", dw2, None if db2 is None else db2.to(b2_dt), split, rank, packed)
                 cfg.cache.limit_compute_sms(True)
+            if W > 1:   # fc1's gradients start their reduction before the input-gradient GEMM is even launched
+                kw["after_dw"] = lambda g, b: cfg.cache.reduce_deferred(stage, "fc1", g, None if b is None else b.to(b1_dt),
+                                                                        split, rank, packed)
             dx, dw1, db1 = be.moe_backward_fc1(st, dh, w1, has_b1=ctx.has_b1, grad_dtype=w1_dt, **kw)
             if W > 1:
                 cfg.cache.release(stage)
-                cfg.cache.reduce_deferred(stage, "fc1", dw1, None if db1 is None else db1.to(b1_dt), split, rank, packed)
                 dw1 = dw2 = db1 = db2 = None
         else:
             sizes = ctx.sizes

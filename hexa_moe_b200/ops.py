@@ -279,11 +279,16 @@ def moe_backward_fc2(st: LayerState, dy, w2, act_id: int, has_b2=True, grad_dtyp
     return dh, dw2, db2
 
 
-def moe_backward_fc1(st: LayerState, dh, w1, has_b1=True, grad_dtype=None, engine=L.ENGINE_AUTO, ranks=1):
-    """Second half: (dx [T,d], dw1 [E,H,d], db1 [E,H] | None) from dh."""
+def moe_backward_fc1(st: LayerState, dh, w1, has_b1=True, grad_dtype=None, engine=L.ENGINE_AUTO, ranks=1,
+                     after_dw=None):
+    """Second half: (dx [T,d], dw1 [E,H,d], db1 [E,H] | None) from dh.  after_dw(dw1, db1), if given, is called on the
+    host as soon as both parameter gradients are enqueued, before the input-gradient GEMM: a caller can start
+    reducing them across ranks while that GEMM runs."""
     r = st.routing
     db1 = ess(dh, r) if has_b1 else None
     dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine, ranks=ranks)
+    if after_dw is not None:
+        after_dw(dw1, db1)
     dxs = esmm(dh, w1, L.B_KN, r, None, L.EPI_LINEAR, engine=engine)
     dx = combine_rows(dxs, r)
     return dx, dw1, db1

@@ -36,7 +36,10 @@ def moe_backward_fc2(st, dy, w2, act_id, has_b2=True, grad_dtype=None, engine=0,
     return None, r["dw2"].to(gd), (r["db2"].float() if has_b2 else None)
 
 
-def moe_backward_fc1(st, dh, w1, has_b1=True, grad_dtype=None, engine=0, ranks=1):
+def moe_backward_fc1(st, dh, w1, has_b1=True, grad_dtype=None, engine=0, ranks=1, after_dw=None):
     r = st.res
     gd = grad_dtype or st.x.dtype
-    return r["dx"].to(st.x.dtype), r["dw1"].to(gd), (r["db1"].float() if has_b1 else None)
+    dw1, db1 = r["dw1"].to(gd), (r["db1"].float() if has_b1 else None)
+    if after_dw is not None:
+        after_dw(dw1, db1)
+    return r["dx"].to(st.x.dtype), dw1, db1
