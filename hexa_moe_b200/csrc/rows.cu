@@ -153,7 +153,7 @@ extern "C" int hexa_gather_rows(const void* src, int64_t src_ld, const int32_t* 
                                 int E, int64_t row_cap, int64_t cols, void* dst, int64_t dst_ld, int dtype,
                                 void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  HEXA_REQUIRE(src && row_token && pad_offsets && dst, "hexa_gather_rows: null pointer");
+  HEXA_REQUIRE(row_token && pad_offsets && dst, "hexa_gather_rows: null pointer");   // src may be null when there are no tokens
   HEXA_REQUIRE(E > 0 && row_cap >= 0 && cols > 0 && src_ld >= cols && dst_ld >= cols, "hexa_gather_rows: bad sizes");
   HEXA_REQUIRE(dtype == HEXA_F32 || dtype == HEXA_F16 || dtype == HEXA_BF16, "hexa_gather_rows: bad dtype %d", dtype);
   if (row_cap == 0) return HEXA_OK;
@@ -175,8 +175,9 @@ extern "C" int hexa_gather_rows(const void* src, int64_t src_ld, const int32_t* 
 extern "C" int hexa_combine_rows(const void* src, int64_t src_ld, const int32_t* token_row, int64_t T, int top_k,
                                  int64_t cols, void* dst, int64_t dst_ld, int dtype, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  HEXA_REQUIRE(src && token_row && dst, "hexa_combine_rows: null pointer");
   HEXA_REQUIRE(T >= 0 && top_k > 0 && cols > 0 && src_ld >= cols && dst_ld >= cols, "hexa_combine_rows: bad sizes");
+  if (T == 0) return HEXA_OK;
+  HEXA_REQUIRE(src && token_row && dst, "hexa_combine_rows: null pointer");
   HEXA_REQUIRE(aligned16(src) && aligned16(dst), "hexa_combine_rows: pointers must be 16-byte aligned");
   if (T == 0) return HEXA_OK;
   const int warps = 8;
