@@ -40,6 +40,8 @@ SIGNATURES = {
     "hexa_esmm": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, vp, i64, vp, i64, vp, vp, vp, vp, ci, i64, i64, i64, ci, ci, ci, ci, vp]),
     "hexa_estmm": (ci, [vp, i64, vp, i64, vp, ci, i64, i64, i64, vp, i64, i64, i64, i64, ci, ci, ci, ci, vp]),
     "hexa_copy_2d": (ci, [vp, i64, vp, i64, i64, i64, vp]),
+    "hexa_stream_wait_value": (ci, [vp, C.c_int32, vp]),
+    "hexa_mean_slices": (ci, [vp, vp, ci, i64, ci, vp, ci, vp]),
     "hexa_ess_workspace_bytes": (sz, [i64, i64]),
     "hexa_ess": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, ci, vp, sz, vp]),
     "hexa_mask_pad_rows": (ci, [vp, i64, vp, vp, ci, i64, i64, ci, vp]),

@@ -296,10 +296,13 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
             # reduce-scatter reads (no packing pass)
             packed = W > 1 and x_is_cuda(dy) and _is_nccl(cfg.group) and all(s_ == split[0] for s_ in split)
             kw = dict(ranks=W) if packed else {}
-            dh, dw2, db2 = be.moe_backward_fc2(st, dy, w2, cfg.act_id, has_b2=ctx.has_b2, grad_dtype=w2_dt, **kw)
+            kw2 = dict(kw, dw_out=cfg.cache.grad_buffer("fc2", stage)) if packed else {}
+            dh, dw2, db2 = be.moe_backward_fc2(st, dy, w2, cfg.act_id, has_b2=ctx.has_b2, grad_dtype=w2_dt, **kw2)
             if W > 1:   # reductions run on the side stream; the results are handed to the parameters when backward ends
                 cfg.cache.reduce_deferred(stage, "fc2", dw2, None if db2 is None else db2.to(b2_dt), split, rank, packed)
-                cfg.cache.limit_compute_sms(True)
+                cfg.cache.limit_compute_sms(cfg.cache.reduce_uses_sms())
+            if packed:
+                kw["dw_out"] = cfg.cache.grad_buffer("fc1", stage)
             if W > 1:   # fc1's gradients start their reduction before the input-gradient GEMM is even launched
                 kw["after_dw"] = lambda g, b: cfg.cache.reduce_deferred(stage, "fc1", g, None if b is None else b.to(b1_dt),
                                                                         split, rank, packed)

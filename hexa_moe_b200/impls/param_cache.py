@@ -35,6 +35,7 @@ class PipelineSharedCache:
         self.side: Optional[torch.cuda.Stream] = None
         self._pending = []
         self._callback_queued = False
+        self._red = None          # peer-copy reduce-scatter state (buffers, flags), built on first use
 
     # -- storage ---------------------------------------------------------------------------------
     def _ensure(self, device, dtype):
@@ -109,6 +110,10 @@ class PipelineSharedCache:
             self._peers = None
             return False
         self._peers, self._peer_ptrs = peers, ptrs
+        if not getattr(self, "_atexit_registered", False):
+            import atexit
+            atexit.register(self.close)      # mappings of other ranks' memory must go before interpreter teardown
+            self._atexit_registered = True
         return True
 
     def _gather_peer(self, slot, stage, order):
@@ -121,7 +126,10 @@ class PipelineSharedCache:
         views = self._views(slot, stage)
         if stage == 0 or self._sync_needed:
             # every rank's parameters are final (its optimizer has run) before anyone reads them
-            dist.all_reduce(self._flag, group=o.group)
+            if self._red not in (None, False):
+                self._peer_barrier()
+            else:
+                dist.all_reduce(self._flag, group=o.group)
             self._sync_needed = False
         for kind in order:
             full = views[kind]
@@ -229,6 +237,106 @@ class PipelineSharedCache:
         ev.record(torch.cuda.current_stream())
         self.slots[stage % 2]["free"] = ev
 
+    # -- reduce-scatter over peer memory (copy engines + stream memory operations, no NCCL kernels) ----------
+    def _reducer_setup(self):
+        """Persistent, IPC-shared buffers for the weight gradients in reduce-scatter layout ([W, E, loc, d], two per
+        kind so consecutive layers alternate), a receive area, and one int32 flag per peer for an SM-free barrier."""
+        if self._red is not None:
+            return self._red is not False
+        o = self.o
+        ok = False
+        try:
+            if not (self._p2p and self._peer_setup()) or os.environ.get("HEXA_P2P_REDUCE", "1") == "0":
+                raise RuntimeError("peer access unavailable")
+            from torch.multiprocessing.reductions import rebuild_cuda_tensor, reduce_tensor
+            dev, dtype = self.side.device, o.batched_fc1_w[0].dtype
+            W, E = o.world_size, o.num_global_experts
+            n1 = max(W * E * o.local_dim_bound_list[i] * o.input_dim_list_moe[i] for i in range(o.total_depth_moe))
+            n2 = max(W * E * o.local_dim_bound_list[i] * o.output_dim_list_moe[i] for i in range(o.total_depth_moe))
+            red = dict(
+                grad=dict(fc1=[torch.empty(n1, device=dev, dtype=dtype) for _ in range(2)],
+                          fc2=[torch.empty(n2, device=dev, dtype=dtype) for _ in range(2)]),
+                recv=torch.empty(max(n1, n2) // W * max(W - 1, 1), device=dev, dtype=dtype),
+                flags=torch.zeros(W, device=dev, dtype=torch.int32),
+                seq_table=torch.arange(1, (1 << 16) + 1, device=dev, dtype=torch.int32), seq=0, seq_base=0, old_tables=[],
+                free={("fc1", 0): None, ("fc1", 1): None, ("fc2", 0): None, ("fc2", 1): None})
+            mine = dict(fc1=[reduce_tensor(t)[1] for t in red["grad"]["fc1"]], fc2=[reduce_tensor(t)[1] for t in red["grad"]["fc2"]],
+                        flags=reduce_tensor(red["flags"])[1])
+            everyone = [None] * W
+            dist.all_gather_object(everyone, mine, group=o.group)
+            red["peer_grad"], red["peer_flags"] = [], []
+            for r, h in enumerate(everyone):
+                if r == o.local_rank:
+                    red["peer_grad"].append(red["grad"]); red["peer_flags"].append(red["flags"])
+                else:
+                    red["peer_grad"].append(dict(fc1=[rebuild_cuda_tensor(*a) for a in h["fc1"]],
+                                                 fc2=[rebuild_cuda_tensor(*a) for a in h["fc2"]]))
+                    red["peer_flags"].append(rebuild_cuda_tensor(*h["flags"]))
+            ok = True
+        except Exception:  # noqa: BLE001
+            red = False
+        flag = torch.tensor([1 if ok else 0], device=self.side.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=o.group)       # all ranks take the same path
+        self._red = red if int(flag.item()) == 1 else False
+        return self._red is not False
+
+    def _peer_barrier(self):
+        """Every rank's side stream has reached this point before any rank's side stream continues.  Each rank copies
+        the next sequence number into its slot of every peer's flag array (4-byte peer copies) and then makes its
+        stream wait until all of its own slots have reached that number."""
+        from .. import ops as _ops
+        red, o = self._red, self.o
+        red["seq"] += 1
+        seq = red["seq"]
+        if seq - red["seq_base"] > red["seq_table"].numel():       # next block of sequence numbers
+            red["old_tables"] = [red["seq_table"]]                 # copies already enqueued may still read it
+            red["seq_base"] = seq - 1
+            red["seq_table"] = torch.arange(seq, seq + (1 << 16), device=red["flags"].device, dtype=torch.int32)
+        val = red["seq_table"][seq - red["seq_base"] - 1: seq - red["seq_base"]]
+        stream = self.side.cuda_stream
+        for r in range(o.world_size):
+            if r != o.local_rank:
+                _ops.copy_2d(red["peer_flags"][r][o.local_rank: o.local_rank + 1], 1, val, 1, 1, 1, stream=stream)
+        for r in range(o.world_size):
+            if r != o.local_rank:
+                _ops.stream_wait_value(red["flags"][r: r + 1], seq, stream)
+
+    def grad_buffer(self, which: str, stage: int):
+        """Where ESTMM should write this layer's weight gradient so that the peer-copy reduce-scatter can read it:
+        a [W, E, loc, d] view of a persistent shared buffer, or None when that path is not in use.  Orders the
+        current stream after the last remote reader of the buffer's previous contents."""
+        if self.side is None or not self._reducer_setup():
+            return None
+        o = self.o
+        W, E, loc = o.world_size, o.num_global_experts, o.local_dim_list[stage]
+        d = o.input_dim_list_moe[stage] if which == "fc1" else o.output_dim_list_moe[stage]
+        ev = self._red["free"][(which, stage % 2)]
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+        return self._red["grad"][which][stage % 2][: W * E * loc * d].view(W, E, loc, d)
+
+    def _reduce_peer(self, which: str, stage: int, out):
+        """Side stream: out[E, loc, d] = mean over ranks of their packed gradient's slice for this rank."""
+        from .. import ops as _ops
+        red, o = self._red, self.o
+        W, rank = o.world_size, o.local_rank
+        n = out.numel()
+        par = stage % 2
+        self._peer_barrier()                                      # every rank's gradient is complete
+        recv = red["recv"][: (W - 1) * n].view(W - 1, n)
+        i = 0
+        for k in range(1, W):
+            r = (rank + k) % W
+            src = red["peer_grad"][r][which][par][rank * n: (rank + 1) * n]
+            _ops.copy_2d(recv[i], n, src, n, n, 1, stream=self.side.cuda_stream)
+            i += 1
+        local = red["grad"][which][par][rank * n: (rank + 1) * n]
+        _ops.mean_slices(local, recv, W - 1, W, out.view(-1))
+        self._peer_barrier()                                      # every rank has finished reading everyone's buffer
+        ev = torch.cuda.Event()
+        ev.record(self.side)
+        red["free"][(which, par)] = ev
+
     # -- gradient reduction ----------------------------------------------------------------------
     def reduce_deferred(self, stage: int, which: str, dw, db, split: List[int], rank: int, packed: bool = False):
         """Average one layer's expert gradients over the ranks without stalling the compute stream.
@@ -244,10 +352,18 @@ class PipelineSharedCache:
             targets = [(o.batched_fc2_w[stage], dw, True), (o.batched_fc2_bias[stage] if o.has_fc2_bias else None, db, False)]
         targets = [t for t in targets if t[0] is not None and t[1] is not None]
 
+        peer_out = None
+        if packed and self._red not in (None, False) and dw is not None and dw.dim() == 4:
+            # allocated on the compute stream: it becomes the parameter's .grad
+            peer_out = dw.new_empty(tuple(dw.shape[1:]))
+
         def run():
             outs = []
             for prm, g, sharded in targets:
-                if sharded and packed and g.dim() == prm.dim() + 1:     # already [W, E, loc, d]
+                if sharded and peer_out is not None and g is dw:
+                    self._reduce_peer(which, stage, peer_out)
+                    outs.append((prm, peer_out))
+                elif sharded and packed and g.dim() == prm.dim() + 1:     # already [W, E, loc, d]
                     outs.append((prm, _layers.reduce_scatter_packed_avg(g, o.group)))
                 elif sharded:
                     outs.append((prm, _layers.reduce_scatter_hidden_avg(g, split, rank, o.group)))
@@ -292,6 +408,23 @@ class PipelineSharedCache:
     def uses_sms(self) -> bool:
         """True when gathers run as NCCL kernels (the peer-copy path leaves every SM to the GEMMs)."""
         return not (self._p2p and self._peers is not None)
+
+    def reduce_uses_sms(self) -> bool:
+        """True when the large gradient reductions run as NCCL kernels."""
+        return self._red in (None, False)
+
+    def close(self):
+        """Drop the mappings of other ranks' memory (call on every rank before the process group is destroyed)."""
+        if self.side is not None:
+            torch.cuda.synchronize()
+        self._pending = []
+        self._peers = None
+        self._peer_ptrs = None
+        self._red = None
+        if self.side is not None:
+            import gc
+            gc.collect()
+            torch.cuda.ipc_collect()      # give the mapped segments back before their owners exit
 
     def limit_compute_sms(self, on: bool):
         """While a collective may be running, keep the persistent GEMM kernels off `HEXA_COMM_SMS` SMs (default 16)

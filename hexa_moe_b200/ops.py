@@ -18,17 +18,17 @@ from ._lib import check, dt, lib, ptr, stream_of
 
 # ---- optional per-call instrumentation (used by bench.py; off by default) --------------------------
 # LAUNCHES counts kernels launched through the C ABI.  When PROFILE is a list, every wrapper appends
-# (name, start_event, end_event, algorithmic_work) with CUDA events recorded on the launching stream.
+# (name, start_event, end_event, algorithmic_work, algorithmic_bytes) with CUDA events recorded on the launching stream.
 LAUNCHES = 0
 PROFILE = None
 _KERNELS_PER_CALL = dict(route=3, gather=1, combine=1, esmm=1, estmm=1, ess=2, mask=1)
 
 
 class _Timed:
-    __slots__ = ("name", "work", "ev")
+    __slots__ = ("name", "work", "bytes", "ev")
 
-    def __init__(self, name, work=0.0):
-        self.name, self.work, self.ev = name, work, None
+    def __init__(self, name, work=0.0, nbytes=0.0):
+        self.name, self.work, self.bytes, self.ev = name, work, nbytes, None
 
     def __enter__(self):
         global LAUNCHES
@@ -42,7 +42,7 @@ class _Timed:
         if self.ev is not None:
             end = torch.cuda.Event(enable_timing=True)
             end.record()
-            PROFILE.append((self.name, self.ev, end, self.work))
+            PROFILE.append((self.name, self.ev, end, self.work, self.bytes))
         return False
 
 
@@ -144,7 +144,10 @@ def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Opti
         raise L.HexaError("esmm: bias must be float32")
     if out is None:
         out = torch.empty(r.row_capacity, n_out, dtype=a.dtype, device=a.device)
-    with _Timed("esmm:%d" % epilogue, 2.0 * r.num_tokens * r.top_k * n_out * k):
+    rows_ = r.num_tokens * r.top_k
+    es_ = a.element_size()
+    nbytes = es_ * (rows_ * k + r.num_experts * n_out * k + rows_ * n_out * (1 if epilogue == L.EPI_LINEAR else 2))
+    with _Timed("esmm:%d" % epilogue, 2.0 * rows_ * n_out * k, float(nbytes)):
         check(lib().hexa_esmm(ptr(a), _ld(a), ptr(b), b_layout, b.stride(1), b.stride(0), ptr(bias),
                               0 if bias is None else _ld(bias), ptr(aux), 0 if aux is None else _ld(aux), ptr(out), _ld(out),
                               ptr(r.tile_expert), ptr(r.pad_offsets), ptr(r.row_token), ptr(r.pair_block), r.num_experts, r.row_capacity,
@@ -177,17 +180,30 @@ def estmm(p: torch.Tensor, q: torch.Tensor, r: Routing, out_dtype: Optional[torc
         ldo, estride, m_split, split_stride = out.stride(1), out.stride(0), 0, 0
     if out.stride(-1) != 1:
         raise L.HexaError("estmm: out must have unit inner stride")
-    with _Timed("estmm", 2.0 * r.num_tokens * r.top_k * m * n):
+    rows_ = r.num_tokens * r.top_k
+    with _Timed("estmm", 2.0 * rows_ * m * n, float(p.element_size() * rows_ * (m + n) + out.element_size() * r.num_experts * m * n)):
         check(lib().hexa_estmm(ptr(p), _ld(p), ptr(q), _ld(q), ptr(r.pad_offsets), r.num_experts, r.row_capacity, m, n, ptr(out),
                                ldo, estride, m_split, split_stride, dt(p), dt(out), beta, engine, stream_of(p)), "hexa_estmm")
     return out
 
 
-def copy_2d(dst: torch.Tensor, dst_pitch: int, src: torch.Tensor, src_pitch: int, width: int, height: int):
-    """Device-to-device copy of `height` blocks of `width` elements (pitches in elements) on the current stream of
-    dst's device; src may live on another GPU (peer memory)."""
+def copy_2d(dst: torch.Tensor, dst_pitch: int, src: torch.Tensor, src_pitch: int, width: int, height: int, stream: int = None):
+    """Device-to-device copy of `height` blocks of `width` elements (pitches in elements).  Runs on `stream` (a raw
+    cudaStream_t) or, by default, on the current stream of dst's device; src or dst may be another GPU's memory."""
     es = src.element_size()
-    check(lib().hexa_copy_2d(ptr(dst), dst_pitch * es, ptr(src), src_pitch * es, width * es, height, stream_of(dst)), "hexa_copy_2d")
+    check(lib().hexa_copy_2d(ptr(dst), dst_pitch * es, ptr(src), src_pitch * es, width * es, height,
+                             stream_of(dst) if stream is None else stream), "hexa_copy_2d")
+
+
+def stream_wait_value(flag: torch.Tensor, value: int, stream: int):
+    """`stream` waits until the int32 at flag[0] is >= value."""
+    check(lib().hexa_stream_wait_value(ptr(flag), value, stream), "hexa_stream_wait_value")
+
+
+def mean_slices(local: torch.Tensor, recv: torch.Tensor, n_recv: int, world: int, out: torch.Tensor):
+    """out = (local + recv[0] + ... + recv[n_recv-1]) / world with fp32 accumulation; all slices shaped like `local`."""
+    check(lib().hexa_mean_slices(ptr(local), ptr(recv), n_recv, local.numel(), world, ptr(out), dt(local), stream_of(out)),
+          "hexa_mean_slices")
 
 
 def ess(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -263,13 +279,14 @@ def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=Fa
     return y, (LayerState(r, xs, y1, h, g) if need_state else None)
 
 
-def moe_backward_fc2(st: LayerState, dy, w2, act_id: int, has_b2=True, grad_dtype=None, engine=L.ENGINE_AUTO, ranks=1):
+def moe_backward_fc2(st: LayerState, dy, w2, act_id: int, has_b2=True, grad_dtype=None, engine=L.ENGINE_AUTO, ranks=1,
+                     dw_out=None):
     """First half of the layer backward: (dh [cap,H] = dy W2^T * act'(y1), dw2 [E,H,d_out], db2 [E,d_out] | None).
     Split from the fc1 half so a caller can start reducing dw2/db2 across ranks while fc1 runs."""
     r = st.routing
     dys = gather_rows(dy.contiguous(), r)
     db2 = ess(dys, r) if has_b2 else None
-    dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine, ranks=ranks)
+    dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine, ranks=ranks, out=dw_out)
     if act_id >= 0:
         dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_DACT, act_id, aux=st.y1, engine=engine)
     else:
@@ -280,13 +297,13 @@ def moe_backward_fc2(st: LayerState, dy, w2, act_id: int, has_b2=True, grad_dtyp
 
 
 def moe_backward_fc1(st: LayerState, dh, w1, has_b1=True, grad_dtype=None, engine=L.ENGINE_AUTO, ranks=1,
-                     after_dw=None):
+                     after_dw=None, dw_out=None):
     """Second half: (dx [T,d], dw1 [E,H,d], db1 [E,H] | None) from dh.  after_dw(dw1, db1), if given, is called on the
     host as soon as both parameter gradients are enqueued, before the input-gradient GEMM: a caller can start
     reducing them across ranks while that GEMM runs."""
     r = st.routing
     db1 = ess(dh, r) if has_b1 else None
-    dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine, ranks=ranks)
+    dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine, ranks=ranks, out=dw_out)
     if after_dw is not None:
         after_dw(dw1, db1)
     dxs = esmm(dh, w1, L.B_KN, r, None, L.EPI_LINEAR, engine=engine)

@@ -187,6 +187,18 @@ size_t hexa_ess_static_capacity_bytes(void);
 int hexa_ess_static(const void* src, int64_t src_ld, const int32_t* pad_offsets, int num_experts,
                     int64_t row_capacity, int64_t cols, float* out, int64_t ldo, int dtype, void* stream);
 
+/* ---- SM-free collectives over NVLink peer memory (no counterpart in the reference, which calls NCCL through
+ *      torch.distributed for everything) ---- */
+
+/* The stream waits until *addr >= value (cuStreamWaitValue32).  With one word per peer, written by the peer with a
+ * 4-byte hexa_copy_2d into this GPU's memory, this is a barrier between ranks that needs no kernel. */
+int hexa_stream_wait_value(const int32_t* addr, int32_t value, void* stream);
+
+/* out[i] = (local[i] + sum_{s<n_recv} recv[s*elems + i]) / world, fp32 accumulation, 16-byte vectors: the reduction
+ * step of a reduce-scatter(AVG) whose transfers were peer copies.  elems must be a multiple of 16/sizeof(dtype). */
+int hexa_mean_slices(const void* local, const void* recv, int n_recv, int64_t elems, int world, void* out, int dtype,
+                     void* stream);
+
 /* Elementwise helper on sorted rows for activations the epilogue does not know:
  * dst[r,:] = row_token[r] >= 0 ? src[r,:] : 0 (restores the zero-pad-row invariant). */
 int hexa_mask_pad_rows(void* buf, int64_t ld, const int32_t* row_token, const int32_t* pad_offsets,

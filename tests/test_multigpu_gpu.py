@@ -90,6 +90,8 @@ def _worker(rank, world, port, data_centric, proportion, dtype_name, q):
                 want = comb(key)[:, lo: lo + n] if sl else comb(key)
                 got = prm.grad[:, :n] if sl else prm.grad
                 assert err(got, want) < tol * 1.5, (i, name, err(got, want))
+        if m.dispatch_params.cache is not None:
+            dist.barrier(); m.dispatch_params.cache.close(); dist.barrier()
         q.put((rank, "ok"))
     except Exception:  # noqa: BLE001
         import traceback
