@@ -130,3 +130,24 @@ def test_unrecognised_activation_uses_the_callable():
                       torch.ones(300, 64))
     assert rel_err(y, res["y"]) < 1e-5 and rel_err(xg.grad, res["dx"]) < 1e-5
     assert rel_err(m.batched_fc1_w[0].grad, res["dw1"]) < 1e-5
+
+
+def test_inference_mode_and_gradient_accumulation():
+    """no_grad forward keeps no state and equals the training forward; two backward passes accumulate into .grad."""
+    torch.manual_seed(2)
+    m = _toy(k=2, d=64, E=4)
+    with torch.no_grad():
+        for n_, p in m.named_parameters():
+            p.normal_(0, 0.3)
+    m = m.bfloat16().cuda().eval()
+    x = torch.randn(3, 100, 64, device="cuda").bfloat16()
+    with torch.no_grad():
+        y0, _ = m(2, x)
+    xg = x.clone().requires_grad_(True)
+    y1, _ = m(2, xg)
+    assert torch.equal(y0, y1)
+    y1.float().sum().backward()
+    g1 = m.batched_fc1_w[0].grad.clone()
+    y2, _ = m(2, xg)
+    y2.float().sum().backward()
+    torch.testing.assert_close(m.batched_fc1_w[0].grad.float(), 2 * g1.float(), rtol=2e-2, atol=1e-3)
