@@ -44,9 +44,11 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the workload's)")
-    ap.add_argument("--workload", default="c5", choices=["c5", "c2", "small"],
+    ap.add_argument("--workload", default="c5", choices=["c5", "c2", "small", "c4"],
                     help="c5: the headline layer; c2: d=768/H=3072/E=32, 16384 tokens (operator-sweep config, sized for ncu "
-                         "captures); small: d=256/H=1024/E=8, 8192 tokens (smoke)")
+                         "captures); small: d=256/H=1024/E=8, 8192 tokens (smoke); c4: the Swin-MoE-B-like network "
+                         "(secondary: images/s through the whole synthetic model, 128 images of 192x192 per GPU)")
+    ap.add_argument("--images", type=int, default=128, help="c4: images per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -164,6 +166,84 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_swin(args, dev, rank, world, timed_factory=None):
+    """Secondary workload: forward + backward of the synthetic Swin-MoE-B-like network (swin_moe_harness.py), bf16,
+    data-centric at N > 1.  One JSON line with images/s and the MoE-layer token rate."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from hexa_moe_b200 import ops
+    from swin_moe_harness import SwinMoEHarness
+    torch.manual_seed(0)
+    m = SwinMoEHarness().to(torch.bfloat16).to(dev).train()
+    for g in m.cascaded_moe.gates:
+        g.gate_noise = 0.0
+    params = list(m.parameters())
+    gen = torch.Generator().manual_seed(99 + rank)
+    imgs_host = torch.randn(args.images, 3, 192, 192, generator=gen).to(torch.bfloat16).pin_memory()
+    labels = torch.randint(0, 1000, (args.images,), generator=gen).to(dev)
+    imgs_dev = imgs_host.to(dev)
+    stage = torch.empty_like(imgs_dev)
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def step(x):
+        for p in params:
+            p.grad = None
+        logits, aux = m(x)
+        loss = F.cross_entropy(logits.float(), labels) + 0.01 * aux
+        loss.backward()
+        return loss
+
+    def step_e2e():
+        stage.copy_(imgs_host, non_blocking=True)
+        loss = step(stage)
+        loss_host.copy_(loss.detach(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def timed(fn, n):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t)
+        return ms / n
+
+    for _ in range(max(args.warmup, 3)):
+        step(imgs_dev)
+    l0 = ops.LAUNCHES
+    ms = timed(lambda: step(imgs_dev), args.steps)
+    launches = ops.LAUNCHES - l0
+    step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    if rank == 0:
+        moe_tokens = sum(m.moe_tokens_per_image()) * args.images * world
+        line = dict(metric="swin_moe_images_per_s", value=args.images * world / (ms * 1e-3), unit="images/s", n_gpus=world,
+                    steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="weak",
+                    vs_baseline=None, dtype="bf16", data="synthetic",
+                    config=dict(workload="c4-swin-moe-b-like", images_per_gpu=args.images, img=192, experts=32, top_k=1,
+                                moe_layers=len(m.moe_idx), mode="data-centric",
+                                note="window attention without shift mask / relative position bias (timing harness)"),
+                    moe_layer_tokens_per_s=moe_tokens / (ms * 1e-3),
+                    e2e=dict(value=args.images * world / (ms_e2e * 1e-3), unit="images/s", ms_per_step=ms_e2e,
+                             h2d_bytes_per_step=imgs_host.numel() * 2, d2h_bytes_per_step=4),
+                    gpu_launches=launches)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        m.cascaded_moe.dispatch_params.cache.close()
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # ------------------------------------------------------------------------------------------------
 def main():
     args = parse()
@@ -195,6 +275,8 @@ def main():
     if world > 1:
         dist.barrier()
 
+    if args.workload == "c4":
+        return run_swin(args, dev, rank, world, timed_factory=None)
     d, H, E, T_default = WORKLOADS[args.workload]
     k, L = TOP_K, LAYERS
     T = args.tokens or T_default

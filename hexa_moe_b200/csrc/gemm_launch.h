@@ -1,0 +1,21 @@
+// Launchers of the GEMM-shaped operators, one set per kernel family (defined in gemm_tc.cu and gemm_simt.cu,
+// selected by the C-ABI entry points in ops_api.cu).  Argument order follows hexa_esmm / hexa_estmm.
+#pragma once
+
+#include "hexa_common.cuh"
+
+namespace hexa {
+int esmm_simt_launch(const void*, int64_t, const void*, int, int64_t, int64_t, const float*, int64_t, void*, int64_t, void*,
+                     int64_t, const int32_t*, const int32_t*, const int32_t*, int, int64_t, int64_t, int64_t, int, int, int,
+                     cudaStream_t);
+int estmm_simt_launch(const void*, int64_t, const void*, int64_t, const int32_t*, int, int64_t, int64_t, void*, int64_t,
+                      int64_t, int64_t, int64_t, int, int, int, cudaStream_t);
+bool esmm_tc_supported(const void*, int64_t, const void*, int64_t, int64_t, const void*, int64_t, const void*, int64_t,
+                       const float*, int64_t, int64_t, int);
+int esmm_tc_launch(const void*, int64_t, const void*, int, int64_t, int64_t, const float*, int64_t, void*, int64_t, void*,
+                   int64_t, const int32_t*, const int32_t*, const int32_t*, const int32_t*, int, int64_t, int64_t, int64_t, int,
+                   int, int, cudaStream_t);
+bool estmm_tc_supported(const void*, int64_t, const void*, int64_t, const void*, int64_t, int64_t, int64_t, int64_t, int, int);
+int estmm_tc_launch(const void*, int64_t, const void*, int64_t, const int32_t*, int, int64_t, int64_t, int64_t, void*, int64_t,
+                    int64_t, int64_t, int64_t, int, int, int, cudaStream_t);
+}  // namespace hexa

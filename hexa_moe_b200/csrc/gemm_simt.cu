@@ -2,6 +2,7 @@
 // These are the kernels for fp32 data (where a 16-bit tensor-core pass cannot meet a 1e-5
 // tolerance) and for shapes the tcgen05 kernels do not take (leading dimensions that are not
 // multiples of 16 bytes).  64x64 output tile, 16-deep k step, 256 threads with a 4x4 micro-tile.
+#include "gemm_launch.h"
 #include "hexa_common.cuh"
 
 namespace hexa {

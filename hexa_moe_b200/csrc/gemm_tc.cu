@@ -31,6 +31,7 @@
 #include <cudaTypedefs.h>
 #include <stdlib.h>
 
+#include "gemm_launch.h"
 #include "hexa_common.cuh"
 
 namespace hexa {

@@ -1,0 +1,124 @@
+"""Synthetic Swin-MoE-like network around MoE_Cascaded, for running the data-centric mode in the setting it was
+designed for: attention blocks between the MoE layers give the pipeline-shared cache something to overlap with.
+
+Shape of the reference's Swin-MoE-B example (Swin-Transformer-MoE/configs/swinmoe/
+swin_moe_base_patch4_window12_192_*.yaml and models/swin_transformer_moe_cascaded.py:650-879): 4x4 patch embedding,
+stage dims 128/256/512/1024 with depths 2/2/18/2 and heads 4/8/16/32, window 12, patch merging between stages,
+every block's FFN served by ONE shared MoE_Cascaded (dense FFN in even blocks, MoE in every other block of stages 3
+and 4: 32 experts, top-1, mlp_ratio 4, no fc1 bias).  What is simplified, because this is a timing harness built
+from stock PyTorch ops and not a model to train: window attention is scaled-dot-product attention over (optionally
+rolled) windows without the shifted-window mask and without the continuous relative position bias.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from hexa_moe import moe as hmoe
+
+
+class WindowAttention(nn.Module):
+    def __init__(self, dim: int, heads: int, window: int, shift: int):
+        super().__init__()
+        self.heads, self.window, self.shift = heads, window, shift
+        self.qkv = nn.Linear(dim, 3 * dim)
+        self.proj = nn.Linear(dim, dim)
+
+    def forward(self, x: torch.Tensor, hw: int) -> torch.Tensor:
+        B, N, C = x.shape
+        w = min(self.window, hw)
+        x = x.view(B, hw, hw, C)
+        if self.shift and w < hw:
+            x = torch.roll(x, shifts=(-self.shift, -self.shift), dims=(1, 2))
+        nw = hw // w
+        x = x.view(B, nw, w, nw, w, C).permute(0, 1, 3, 2, 4, 5).reshape(B * nw * nw, w * w, C)
+        q, k, v = self.qkv(x).view(-1, w * w, 3, self.heads, C // self.heads).permute(2, 0, 3, 1, 4)
+        o = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(-1, w * w, C)
+        o = self.proj(o).view(B, nw, nw, w, w, C).permute(0, 1, 3, 2, 4, 5).reshape(B, hw, hw, C)
+        if self.shift and w < hw:
+            o = torch.roll(o, shifts=(self.shift, self.shift), dims=(1, 2))
+        return o.reshape(B, N, C)
+
+
+class Block(nn.Module):
+    """Attention half of a Swin block; returns (norm2(x), shortcut) like the reference's blocks (…:403-407) so that
+    the caller can run the FFN / MoE of this depth through the shared MoE_Cascaded."""
+
+    def __init__(self, dim, heads, window, shift):
+        super().__init__()
+        self.norm1, self.norm2 = nn.LayerNorm(dim), nn.LayerNorm(dim)
+        self.attn = WindowAttention(dim, heads, window, shift)
+
+    def forward(self, x, hw):
+        x = x + self.attn(self.norm1(x), hw)
+        return self.norm2(x), x
+
+
+class PatchMerging(nn.Module):
+    def __init__(self, dim):
+        super().__init__()
+        self.norm = nn.LayerNorm(4 * dim)
+        self.reduction = nn.Linear(4 * dim, 2 * dim, bias=False)
+
+    def forward(self, x, hw):
+        B, N, C = x.shape
+        x = x.view(B, hw // 2, 2, hw // 2, 2, C).permute(0, 1, 3, 2, 4, 5).reshape(B, (hw // 2) ** 2, 4 * C)
+        return self.reduction(self.norm(x))
+
+
+class SwinMoEHarness(nn.Module):
+    def __init__(self, img_size=192, patch=4, dims=(128, 256, 512, 1024), depths=(2, 2, 18, 2), heads=(4, 8, 16, 32),
+                 window=12, num_experts=32, top_k=1, moe_stages=(2, 3), num_classes=1000, data_centric=True,
+                 mlp_proportion=None):
+        super().__init__()
+        self.hw0 = img_size // patch
+        self.patch_embed = nn.Conv2d(3, dims[0], kernel_size=patch, stride=patch)
+        self.embed_norm = nn.LayerNorm(dims[0])
+        blocks, merges, dim_list, moe_idx, self.stage_of = [], [], [], [], []
+        depth = 0
+        for s, (d, n, h) in enumerate(zip(dims, depths, heads)):
+            for i in range(n):
+                blocks.append(Block(d, h, window, shift=(window // 2 if i % 2 else 0)))
+                dim_list.append(d)
+                self.stage_of.append(s)
+                if s in moe_stages and i % 2 == 1:       # every other block of the MoE stages
+                    moe_idx.append(depth)
+                depth += 1
+            merges.append(PatchMerging(d) if s + 1 < len(dims) else nn.Identity())
+        self.blocks, self.merges = nn.ModuleList(blocks), nn.ModuleList(merges)
+        self.depths, self.total_depth, self.moe_idx = list(depths), depth, moe_idx
+        self.cascaded_moe = hmoe.MoE_Cascaded(
+            gate_type={'type': 'top', 'k': top_k, 'fp32_gate': True}, model_dim_list=dim_list, moe_idx_list=moe_idx,
+            mlp_ratio=4, mlp_proportion=mlp_proportion, num_global_experts=num_experts, total_depth=depth,
+            data_centric=data_centric, mlp_fc1_bias=False, mlp_fc2_bias=True, activation_fn=lambda t: F.gelu(t))
+        self.norm = nn.LayerNorm(dims[-1])
+        self.head = nn.Linear(dims[-1], num_classes)
+
+    def moe_tokens_per_image(self) -> List[int]:
+        """Tokens per image entering each MoE layer."""
+        out = []
+        for d in self.moe_idx:
+            hw = self.hw0 // (2 ** self.stage_of[d])
+            out.append(hw * hw)
+        return out
+
+    def forward(self, images: torch.Tensor):
+        x = self.patch_embed(images).flatten(2).transpose(1, 2)
+        x = self.embed_norm(x)
+        hw, depth, l_aux = self.hw0, 0, 0.0
+        for s, n in enumerate(self.depths):
+            for _ in range(n):
+                y, shortcut = self.blocks[depth](x, hw)
+                y, aux = self.cascaded_moe(depth, y)
+                x = shortcut + y
+                if aux is not None:
+                    l_aux = l_aux + aux
+                depth += 1
+            if not isinstance(self.merges[s], nn.Identity):
+                x = self.merges[s](x, hw)
+                hw //= 2
+        x = self.norm(x).mean(dim=1)
+        return self.head(x), l_aux

@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this directory from the UNMODIFIED reference sources.
 
-Run once, in a container that has the reference checkout (default /root/reference) and triton:
+Run once, on a machine that has a checkout of the reference (UNITES-Lab/HEXA-MoE) and triton:
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py --ref <path to the HEXA-MoE checkout>
 
 The reference's Triton kernels are executed on CPU tensors with TRITON_INTERPRET=1.  Three tiny
 import shims (an empty `constant` namespace, an attribute-dict `easydict.EasyDict`, and
@@ -64,7 +64,8 @@ def routing_cases():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("HEXA_MOE_REFERENCE", "reference"),
+                    help="path of the HEXA-MoE checkout (or set HEXA_MOE_REFERENCE)")
     args = ap.parse_args()
     shim = tempfile.mkdtemp(prefix="hexa_shims_")
     write_shims(shim)
