@@ -6,6 +6,7 @@ names are kept (`wg.weight`; `temperature`, `cosine_projector.*`, `sim_matrix`) 
 dicts are interchangeable.  Both accept only `capacity_factor` and `gate_noise` as extra options.
 """
 import math
+import os
 
 import torch
 import torch.nn.functional as F
@@ -15,6 +16,50 @@ def _check_options(options):
     for opt in options:
         if opt not in ("capacity_factor", "gate_noise"):
             raise Exception("Unrecognized argument provided to Gating module: %s" % opt)
+
+
+def _split_terms(t, dtype, n):
+    """t (fp32) as n tensors of `dtype` whose sum reproduces t: each term is the rounding of what the previous ones
+    left over.  Three bf16 terms carry 24 mantissa bits, i.e. all of an fp32 value."""
+    terms, rest = [], t
+    for _ in range(n):
+        p = rest.to(dtype)
+        terms.append(p)
+        rest = rest - p.float()
+    return terms
+
+
+class _SplitPrecisionLinear(torch.autograd.Function):
+    """logits = x W^T for bf16 tokens x [T,d] and an fp32 gate weight W [E,d], with fp32-GEMM accuracy but on the
+    tensor cores and without materialising an fp32 copy of the tokens.
+
+    x is exact in bf16 and W = hi + mid + lo exactly, so one bf16 GEMM against the stacked terms [3E,d] with fp32
+    accumulation yields three partial logits whose sum differs from an fp32 GEMM only by summation order.  Backward
+    does the same for the fp32 logit gradient: dW = sum of three (term^T x) products, and the token gradient, which
+    leaves in bf16 anyway, keeps the leading cross terms (hi*hi + lo*hi + hi*mid)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        E = w.shape[0]
+        w_terms = torch.cat(_split_terms(w.detach(), x.dtype, 3), dim=0)            # [3E, d]
+        part = torch.mm(x, w_terms.t(), out_dtype=torch.float32)                    # [T, 3E]
+        ctx.save_for_backward(x, w_terms)
+        return (part[:, :E] + part[:, E:2 * E]) + part[:, 2 * E:]
+
+    @staticmethod
+    def backward(ctx, dlogits):
+        x, w_terms = ctx.saved_tensors
+        E = w_terms.shape[0] // 3
+        dx = dw = None
+        g_terms = _split_terms(dlogits.float(), x.dtype, 3)
+        if ctx.needs_input_grad[1]:
+            part = torch.mm(torch.cat(g_terms, dim=1).t(), x, out_dtype=torch.float32)   # [3E, d]
+            dw = (part[:E] + part[E:2 * E]) + part[2 * E:]
+        if ctx.needs_input_grad[0]:
+            g = torch.cat([g_terms[0], g_terms[1], g_terms[0]], dim=1)              # [T, 3E]
+            w = torch.cat([w_terms[:E], w_terms[:E], w_terms[E:2 * E]], dim=0)      # [3E, d]
+            dx = torch.mm(g, w)
+        return dx, dw
 
 
 class LinearTopKGate(torch.nn.Module):
@@ -30,6 +75,9 @@ class LinearTopKGate(torch.nn.Module):
 
     def forward(self, x):
         wg = self.wg.float() if self.fp32_gate else self.wg
+        if (self.fp32_gate and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2
+                and os.environ.get("HEXA_SPLIT_GATE", "1") != "0"):
+            return _SplitPrecisionLinear.apply(x, wg.weight)
         return wg(x.to(dtype=wg.weight.dtype))
 
 

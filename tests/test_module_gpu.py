@@ -151,3 +151,32 @@ def test_inference_mode_and_gradient_accumulation():
     y2, _ = m(2, xg)
     y2.float().sum().backward()
     torch.testing.assert_close(m.batched_fc1_w[0].grad.float(), 2 * g1.float(), rtol=2e-2, atol=1e-3)
+
+
+def test_split_precision_gate_matches_an_fp32_projection():
+    """The bf16-token fast path of the fp32 gate (three bf16 terms of the fp32 weight, fp32 accumulation) against a
+    float64 projection: logits and the weight gradient to fp32-GEMM accuracy (2e-5 of the largest value; a plain
+    bf16 weight would be off by 4e-3), the token gradient to its own bf16 rounding (2^-8)."""
+    from hexa_moe_b200.impls.gating import LinearTopKGate
+    torch.manual_seed(3)
+    g = LinearTopKGate(256, 16, k=2, fp32_gate=True).cuda()
+    with torch.no_grad():
+        g.wg.weight.normal_(0, 0.3)
+    x = torch.randn(1000, 256, device="cuda").bfloat16().requires_grad_()
+    logits = g(x)
+    assert logits.dtype == torch.float32
+    xr = x.detach().double().requires_grad_()
+    wr = g.wg.weight.detach().double().requires_grad_()
+    ref = xr @ wr.t()
+    assert float((logits.double() - ref).abs().max()) <= 2e-5 * float(ref.abs().max())
+    dl = torch.randn_like(logits)
+    logits.backward(dl)
+    ref.backward(dl.double())
+    assert float((g.wg.weight.grad.double() - wr.grad).abs().max()) <= 2e-5 * float(wr.grad.abs().max())
+    assert float((x.grad.double() - xr.grad).abs().max()) <= 2.0 ** -8 * float(xr.grad.abs().max())
+    os.environ["HEXA_SPLIT_GATE"] = "0"
+    try:
+        plain = g(x.detach())
+    finally:
+        del os.environ["HEXA_SPLIT_GATE"]
+    assert float((plain - logits).abs().max()) <= 2e-5 * float(ref.abs().max())
