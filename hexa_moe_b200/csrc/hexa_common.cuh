@@ -106,17 +106,21 @@ __device__ __forceinline__ float rcp_fast(float x) {   // one MUFU.RCP, ~1 ulp; 
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ void gelu_parts(float x, float& s, float& e) {
-  // s = 1 + erf(x / sqrt2) (so gelu = 0.5 x s), e = exp(-x^2 / 2)
-  e = __expf(-0.5f * x * x);
-  const float z = fabsf(x) * 0.70710678118654752f;
-  const float t = rcp_fast(fmaf(0.3275911f, z, 1.0f));
-  float q = fmaf(1.061405429f, t, -1.453152027f);
-  q = fmaf(q, t, 1.421413741f);
-  q = fmaf(q, t, -0.284496736f);
-  q = fmaf(q, t, 0.254829592f);
-  q = q * t * e;                      // 1 - erf(|x| / sqrt2)
-  s = x >= 0.f ? 2.0f - q : q;
+__device__ __forceinline__ float ex2_fast(float x) {   // one MUFU.EX2
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// u = (1 - erf(|x| / sqrt2)) / 2 = the Gaussian tail mass beyond |x|, e = exp(-x^2 / 2).  The 1/sqrt2 of the erf
+// argument and the final 1/2 are folded into the constants.
+__device__ __forceinline__ void gelu_parts(float x, float& u, float& e) {
+  e = ex2_fast(x * x * -0.72134752044448170f);            // exp(-x^2/2) = 2^(-x^2 / (2 ln 2))
+  const float t = rcp_fast(fmaf(0.3275911f * 0.70710678118654752f, fabsf(x), 1.0f));
+  float q = fmaf(0.5f * 1.061405429f, t, 0.5f * -1.453152027f);
+  q = fmaf(q, t, 0.5f * 1.421413741f);
+  q = fmaf(q, t, 0.5f * -0.284496736f);
+  q = fmaf(q, t, 0.5f * 0.254829592f);
+  u = q * t * e;
 }
 __device__ __forceinline__ float tanh_fast(float x) {
   float y;
@@ -126,14 +130,23 @@ __device__ __forceinline__ float tanh_fast(float x) {
 
 template <int ACT> __device__ __forceinline__ float act_fast(float x) {
   if (ACT == HEXA_ACT_RELU) return fmaxf(x, 0.f);
-  if (ACT == HEXA_ACT_GELU) { float s, e; gelu_parts(x, s, e); return 0.5f * x * s; }
+  if (ACT == HEXA_ACT_GELU) {
+    // x Phi(x) with Phi = 1 - u for x >= 0 and u for x < 0: both cases are max(x, 0) - |x u|, no compare or select
+    float u, e;
+    gelu_parts(x, u, e);
+    return fmaxf(x, 0.f) - fabsf(x * u);
+  }
   if (ACT == HEXA_ACT_GELU_TANH) return 0.5f * x * (1.f + tanh_fast(0.7978845608028654f * fmaf(0.044715f * x * x, x, x)));
   if (ACT == HEXA_ACT_SILU) return x * rcp_fast(1.f + __expf(-x));
   return x;
 }
 template <int ACT> __device__ __forceinline__ float act_grad_fast(float x) {
   if (ACT == HEXA_ACT_RELU) return x > 0.f ? 1.f : 0.f;
-  if (ACT == HEXA_ACT_GELU) { float s, e; gelu_parts(x, s, e); return fmaf(x * e, 0.3989422804014327f, 0.5f * s); }
+  if (ACT == HEXA_ACT_GELU) {   // Phi(x) + x phi(x)
+    float u, e;
+    gelu_parts(x, u, e);
+    return fmaf(x * e, 0.3989422804014327f, x >= 0.f ? 1.0f - u : u);
+  }
   if (ACT == HEXA_ACT_GELU_TANH) {
     const float x2 = x * x;
     const float t = tanh_fast(0.7978845608028654f * fmaf(0.044715f * x2, x, x));
