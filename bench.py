@@ -219,9 +219,13 @@ def run_swin(args, dev, rank, world, timed_factory=None):
 
     for _ in range(max(args.warmup, 3)):
         step(imgs_dev)
+    sampler = ClockSampler(dev.index or 0) if rank == 0 else None
+    if sampler:
+        sampler.start()
     l0 = ops.LAUNCHES
     ms = timed(lambda: step(imgs_dev), args.steps)
     launches = ops.LAUNCHES - l0
+    clocks = sampler.stop() if sampler else None
     step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
     if rank == 0:
@@ -235,7 +239,7 @@ def run_swin(args, dev, rank, world, timed_factory=None):
                     moe_layer_tokens_per_s=moe_tokens / (ms * 1e-3),
                     e2e=dict(value=args.images * world / (ms_e2e * 1e-3), unit="images/s", ms_per_step=ms_e2e,
                              h2d_bytes_per_step=imgs_host.numel() * 2, d2h_bytes_per_step=4),
-                    gpu_launches=launches)
+                    gpu_launches=launches, clocks=clocks)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

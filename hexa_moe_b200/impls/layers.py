@@ -18,10 +18,13 @@ Differences from the reference, all deliberate:
   * data-centric expert gradients are reduce-scattered (AVG) along the hidden dimension instead of
     all-reduced at full size and sliced (layers.py:431-474) - the same values, 1/W of the traffic;
   * model-centric token gradients are reduce-scattered over the token dimension; the reference
-    sends its local slice to every destination (layers.py:392-396).
+    sends its local slice to every destination (layers.py:392-396);
+  * the dense FFN of 16-bit CUDA tokens runs as a one-expert layer on the same kernels (fused bias,
+    activation and activation derivative); other inputs keep the PyTorch-op formulation.
 """
 from __future__ import annotations
 
+import os
 from typing import Any, List, Optional
 
 import torch
@@ -164,8 +167,19 @@ def _cast(w: Optional[Tensor], dtype) -> Optional[Tensor]:
 
 
 # ------------------------------------------------------------------------------------------------
-# dense FFN (plain PyTorch; the layers either side of every MoE layer)
+# dense FFN (the layers either side of every MoE layer)
 # ------------------------------------------------------------------------------------------------
+def _dense_on_kernels(cfg, x: Tensor) -> bool:
+    """16-bit CUDA tokens with an activation the GEMM epilogue knows run as a one-expert layer on the grouped-GEMM
+    kernels (fused bias + activation, fused activation derivative); anything else is plain PyTorch."""
+    if os.environ.get("HEXA_DENSE_KERNELS", "1") == "0":        # A/B switch: keep the dense FFN on PyTorch ops
+        return False
+    return (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and getattr(cfg, "act_id", -1) >= 0
+            and getattr(cfg, "backend", None) is not None and hasattr(cfg.backend, "dense_forward")
+            and x.shape[0] > 0 and x.shape[1] % 8 == 0
+            and x.shape[1] >= int(os.environ.get("HEXA_DENSE_MIN_DIM", "512")))
+
+
 class MLP_Implement(torch.autograd.Function):
     """y = act(x fc1_w^T + b1) fc2_w + b2 with fc1_w [H,d], fc2_w [H,d_out]; weight and bias gradients are
     averaged over the data-parallel ranks inside backward (reference layers.py:18-88)."""
@@ -175,11 +189,22 @@ class MLP_Implement(torch.autograd.Function):
         ctx.config = config
         assert tokens_input.shape[1] == fc1_w.shape[1] and fc1_w.shape[0] == fc2_w.shape[0]
         dtype = tokens_input.dtype
+        ctx.has_b1, ctx.has_b2 = fc1_bias is not None, fc2_bias is not None
+        ctx.fused = _dense_on_kernels(config, tokens_input) and fc1_w.shape[0] % 8 == 0 and fc2_w.shape[1] % 8 == 0
+        if ctx.fused:
+            x = tokens_input.contiguous()
+            w1, w2 = _cast(fc1_w.detach(), dtype), _cast(fc2_w.detach(), dtype)
+            y, st = config.backend.dense_forward(x, w1, w2, None if fc1_bias is None else fc1_bias.detach(),
+                                                 None if fc2_bias is None else fc2_bias.detach(), config.act_id,
+                                                 need_state=any(ctx.needs_input_grad))
+            ctx.state, ctx.w = st, (w1, w2)
+            ctx.param_dtypes = (fc1_w.dtype, fc2_w.dtype, None if fc1_bias is None else fc1_bias.dtype,
+                                None if fc2_bias is None else fc2_bias.dtype)
+            return y
         hid = tokens_input @ fc1_w.to(dtype).t()
         if fc1_bias is not None:
             hid = hid + fc1_bias.to(dtype)
         ctx.save_for_backward(tokens_input, hid, fc1_w, fc2_w)
-        ctx.has_b1, ctx.has_b2 = fc1_bias is not None, fc2_bias is not None
         y = config.activation_fn(hid) @ fc2_w.to(dtype)
         if fc2_bias is not None:
             y = y + fc2_bias.to(dtype)
@@ -187,21 +212,31 @@ class MLP_Implement(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx: Any, dy: Tensor):
-        x, hid, fc1_w, fc2_w = ctx.saved_tensors
         cfg = ctx.config
-        with torch.enable_grad():
-            hh = hid.detach().requires_grad_(True)
-            act = cfg.activation_fn(hh)
-            (dact,) = torch.autograd.grad(act.sum(), hh)
-        act = act.detach()
-        dtype = dy.dtype
-        d_act = dy @ fc2_w.to(dtype).t()
-        dw2 = (act.t() @ dy).to(fc2_w.dtype)
-        db2 = dy.sum(0).to(fc2_w.dtype) if ctx.has_b2 else None
-        d_hid = d_act * dact
-        dx = d_hid @ fc1_w.to(dtype)
-        dw1 = (d_hid.t() @ x).to(fc1_w.dtype)
-        db1 = d_hid.sum(0).to(fc1_w.dtype) if ctx.has_b1 else None
+        if ctx.fused:
+            (w1, w2), st = ctx.w, ctx.state
+            ctx.state = ctx.w = None
+            dx, dw1, dw2, db1, db2 = cfg.backend.dense_backward(st, dy.contiguous(), w1, w2, cfg.act_id,
+                                                                has_b1=ctx.has_b1, has_b2=ctx.has_b2)
+            pd = ctx.param_dtypes
+            dw1, dw2 = dw1.to(pd[0]), dw2.to(pd[1])
+            db1 = None if db1 is None else db1.to(pd[2])
+            db2 = None if db2 is None else db2.to(pd[3])
+        else:
+            x, hid, fc1_w, fc2_w = ctx.saved_tensors
+            with torch.enable_grad():
+                hh = hid.detach().requires_grad_(True)
+                act = cfg.activation_fn(hh)
+                (dact,) = torch.autograd.grad(act.sum(), hh)
+            act = act.detach()
+            dtype = dy.dtype
+            d_act = dy @ fc2_w.to(dtype).t()
+            dw2 = (act.t() @ dy).to(fc2_w.dtype)
+            db2 = dy.sum(0).to(fc2_w.dtype) if ctx.has_b2 else None
+            d_hid = d_act * dact
+            dx = d_hid @ fc1_w.to(dtype)
+            dw1 = (d_hid.t() @ x).to(fc1_w.dtype)
+            db1 = d_hid.sum(0).to(fc1_w.dtype) if ctx.has_b1 else None
         for g in (dw2, db2, dw1, db1):
             if g is not None:
                 all_reduce_avg(g, cfg.group)

@@ -318,3 +318,58 @@ def moe_backward(st: LayerState, dy, w1, w2, act_id: int, has_b1=True, has_b2=Tr
     dh, dw2, db2 = moe_backward_fc2(st, dy, w2, act_id, has_b2, grad_dtype, engine)
     dx, dw1, db1 = moe_backward_fc1(st, dh, w1, has_b1, grad_dtype, engine)
     return dx, dw1, dw2, db1, db2
+
+
+# -------------------------------------------------------------------------------------------------
+# the dense FFN as a one-expert layer on the same kernels
+# -------------------------------------------------------------------------------------------------
+_DENSE_ROUTING = {}
+
+
+def dense_routing(num_tokens: int, device: torch.device) -> Routing:
+    """Routing of `num_tokens` rows to a single expert: sorted row i is token i, the tail up to the next multiple
+    of 128 is padding.  Built once per (size, device) by the routing kernel itself and kept."""
+    key = (int(num_tokens), device.index if device.index is not None else torch.cuda.current_device())
+    r = _DENSE_ROUTING.get(key)
+    if r is None:
+        if len(_DENSE_ROUTING) >= 64:
+            _DENSE_ROUTING.clear()
+        r = route(torch.zeros(num_tokens, 1, dtype=torch.int32, device=device), 1, L.ROW_TILE)
+        _DENSE_ROUTING[key] = r
+    return r
+
+
+def _dense_rows(t: torch.Tensor, r: Routing) -> torch.Tensor:
+    """t [T, c] as the [row_capacity, c] operand of the grouped GEMMs: t itself when T is a multiple of 128."""
+    if r.row_capacity == t.shape[0] and t.is_contiguous():
+        return t
+    return gather_rows(t.contiguous(), r)
+
+
+def dense_forward(x, w1, w2, b1, b2, act_id: int, need_state=True, engine=L.ENGINE_AUTO):
+    """y = act(x w1^T + b1) w2 + b2 with w1 [H,d], w2 [H,d_out] (the layout of the dense FFN parameters): the MoE
+    layer with one expert and the identity routing, so the activation, both biases and the pad handling are the
+    fused epilogues of the grouped GEMM.  Returns (y [T,d_out], LayerState)."""
+    T = x.shape[0]
+    r = dense_routing(T, x.device)
+    xs = _dense_rows(x, r)
+    y1 = torch.empty(r.row_capacity, w1.shape[0], dtype=x.dtype, device=x.device)
+    h = esmm(xs, w1.unsqueeze(0), L.B_NK, r, None if b1 is None else _f32(b1).view(1, -1), L.EPI_ACT, act_id, aux=y1,
+             engine=engine)
+    ys = esmm(h, w2.unsqueeze(0), L.B_KN, r, None if b2 is None else _f32(b2).view(1, -1), L.EPI_LINEAR, engine=engine)
+    return ys[:T], (LayerState(r, xs, y1, h, None) if need_state else None)
+
+
+def dense_backward(st: LayerState, dy, w1, w2, act_id: int, has_b1=True, has_b2=True, grad_dtype=None, engine=L.ENGINE_AUTO):
+    """Gradients of dense_forward: (dx [T,d], dw1 [H,d], dw2 [H,d_out], db1 [H] | None, db2 [d_out] | None);
+    bias gradients are float32."""
+    r = st.routing
+    T = r.num_tokens
+    dys = _dense_rows(dy, r)
+    db2 = ess(dys, r).view(-1) if has_b2 else None
+    dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine)[0]
+    dh = esmm(dys, w2.unsqueeze(0), L.B_NK, r, None, L.EPI_DACT, act_id, aux=st.y1, engine=engine)
+    db1 = ess(dh, r).view(-1) if has_b1 else None
+    dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine)[0]
+    dxs = esmm(dh, w1.unsqueeze(0), L.B_KN, r, None, L.EPI_LINEAR, engine=engine)
+    return dxs[:T], dw1, dw2, db1, db2

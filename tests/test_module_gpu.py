@@ -180,3 +180,53 @@ def test_split_precision_gate_matches_an_fp32_projection():
     finally:
         del os.environ["HEXA_SPLIT_GATE"]
     assert float((plain - logits).abs().max()) <= 2e-5 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("dtype,tokens", [(torch.bfloat16, 96), (torch.bfloat16, 256), (torch.float16, 200)])
+def test_dense_ffn_on_the_grouped_gemm_kernels(dtype, tokens):
+    """A dense depth of MoE_Cascaded (reference layers.py:18-88) runs as a one-expert layer on the grouped-GEMM
+    kernels for 16-bit tokens.  Checked against a float64 evaluation of the same FFN (2e-2 relative to the largest
+    value, the 16-bit tolerance) and against the PyTorch-op path of the same module, for token counts that are and
+    are not multiples of the 128-row tile."""
+    torch.manual_seed(5)
+    d, E = 64, 4
+    m = _toy(k=1, d=d, E=E)
+    with torch.no_grad():
+        for n_, p in m.named_parameters():
+            if n_.startswith("mlp_fc"):
+                p.normal_(0, 0.1)
+    m = m.to(dtype).cuda().train()
+    x = torch.randn(tokens, d, device="cuda").to(dtype)
+    dy = torch.randn(tokens, d, device="cuda").to(dtype)
+    names = ["mlp_fc1_w.0", "mlp_fc2_w.0", "mlp_fc1_b.0", "mlp_fc2_b.0"]
+    params = dict(m.named_parameters())
+
+    def run():
+        for p in m.parameters():
+            p.grad = None
+        xi = x.clone().requires_grad_(True)
+        y, aux = m(0, xi)
+        assert aux == 0
+        y.backward(dy)
+        return [y.detach(), xi.grad] + [params[n_].grad.clone() for n_ in names]
+
+    from hexa_moe_b200 import ops
+    before = ops.LAUNCHES
+    got = run()
+    assert ops.LAUNCHES - before >= 9, "the dense depth did not run on this library's kernels"
+    os.environ["HEXA_DENSE_KERNELS"] = "0"
+    try:
+        before = ops.LAUNCHES
+        plain = run()
+        assert ops.LAUNCHES == before
+    finally:
+        del os.environ["HEXA_DENSE_KERNELS"]
+    w1, w2, b1, b2 = [params[n_].detach().double().requires_grad_(True) for n_ in names]
+    xr = x.double().requires_grad_(True)
+    yr = F.gelu(xr @ w1.t() + b1) @ w2 + b2
+    yr.backward(dy.double())
+    want = [yr.detach(), xr.grad, w1.grad, w2.grad, b1.grad, b2.grad]
+    for g, p_, w in zip(got, plain, want):
+        assert g.shape == w.shape
+        assert rel_err(g, w) <= 2e-2
+        assert rel_err(g, p_) <= 3e-2
