@@ -45,6 +45,10 @@ SIGNATURES = {
     "hexa_ess_workspace_bytes": (sz, [i64, i64]),
     "hexa_ess": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, ci, vp, sz, vp]),
     "hexa_mask_pad_rows": (ci, [vp, i64, vp, vp, ci, i64, i64, ci, vp]),
+    "hexa_gate_max_experts": (ci, []),
+    "hexa_gate_workspace_bytes": (sz, []),
+    "hexa_gate_topk": (ci, [vp, i64, i64, ci, ci, vp, vp, vp, vp, vp, sz, vp]),
+    "hexa_gate_loss_grad": (ci, [vp, i64, i64, ci, vp, vp, vp, i64, vp]),
     "hexa_ess_static_capacity_bytes": (sz, []),
     "hexa_ess_static": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, ci, vp]),
 }

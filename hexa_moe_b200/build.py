@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libhexa_moe_b200.so")
-SOURCES = ["route.cu", "rows.cu", "gemm_simt.cu", "gemm_tc.cu", "ops_api.cu", "peer.cu"]
+SOURCES = ["route.cu", "rows.cu", "gemm_simt.cu", "gemm_tc.cu", "ops_api.cu", "peer.cu", "gate.cu"]
 
 
 def _nvcc():

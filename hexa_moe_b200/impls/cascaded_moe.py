@@ -35,7 +35,7 @@ from torch.nn import ModuleList, Parameter, ParameterList
 from .. import _lib as L
 from . import losses
 from .activations import classify
-from .gating import GATES
+from .gating import GATES, fused_topk_gshard
 from .layers import FusedMoE_Shared_CudaCore, MLP_Implement, simplified_extract_critical
 from .param_cache import PipelineSharedCache
 
@@ -330,6 +330,10 @@ class MoE_Cascaded(torch.nn.Module):
             logits_w_noise = logits + gate.gate_noise * torch.randn_like(logits) / self.num_global_experts
         else:
             logits_w_noise = logits
+        if self.is_gshard_loss:
+            fused = fused_topk_gshard(logits_w_noise, top_k, getattr(self.dispatch_params, "backend", None))
+            if fused is not None:
+                return fused
         scores = F.softmax(logits_w_noise, dim=1)
         if self.is_gshard_loss:
             loss_fn = losses.gshard_loss

@@ -1,9 +1,12 @@
-"""Router networks of the MoE layers (plain PyTorch: a d x E projection is not kernel work).
+"""Router networks of the MoE layers, and the fused softmax / top-k / GShard-loss step that follows them.
 
 Two gate types, selected by gate_type['type'] exactly as in the reference ('top' and
 'cosine_top', hexa_moe/gates/top.py:6-25 and hexa_moe/gates/cosine_top.py:7-37).  Parameter
 names are kept (`wg.weight`; `temperature`, `cosine_projector.*`, `sim_matrix`) so that state
 dicts are interchangeable.  Both accept only `capacity_factor` and `gate_noise` as extra options.
+
+The projections themselves are library GEMMs (a d x E product is not kernel work); what follows the logits
+(softmax, top-k, the int32 route-major ids, the GShard loss and its gradient) is two kernels of this library.
 """
 import math
 import os
@@ -102,6 +105,40 @@ class CosineTopKGate(torch.nn.Module):
             x, proj, sim = x.float(), proj.float(), sim.float()
         logits = torch.matmul(F.normalize(proj(x), dim=1), F.normalize(sim, dim=0))
         return logits * torch.clamp(self.temperature, max=self.clamp_max).exp()
+
+
+class _TopKWithGShardLoss(torch.autograd.Function):
+    """(ids int32 [k,T], l_aux) from float32 logits [T,E]: softmax, top-k and the GShard loss in one kernel, and the
+    loss gradient in another (softmax recomputed, no [T,E] scores kept).  Same values as
+    F.softmax -> torch.topk -> gshard_loss (reference cascaded_moe.py:568-598, losses.py:12-19) up to the summation
+    order of the loss; ties between equal scores go to the lowest expert id."""
+
+    @staticmethod
+    def forward(ctx, logits, top_k, backend):
+        ids, loss, first_count, _ = backend.gate_topk(logits, top_k)
+        ctx.backend = backend
+        ctx.save_for_backward(logits, first_count)
+        ctx.mark_non_differentiable(ids)
+        return ids, loss
+
+    @staticmethod
+    def backward(ctx, _d_ids, d_loss):
+        if d_loss is None:
+            return None, None, None
+        logits, first_count = ctx.saved_tensors
+        return ctx.backend.gate_loss_grad(logits, first_count, d_loss), None, None
+
+
+def fused_topk_gshard(logits, top_k, backend):
+    """The fused path when it applies (float32 CUDA logits, expert count within the kernel's limit), else None."""
+    if (backend is None or not hasattr(backend, "gate_topk") or not logits.is_cuda or logits.dtype != torch.float32
+            or logits.dim() != 2 or os.environ.get("HEXA_FUSED_GATE", "1") == "0"):
+        return None
+    E = logits.shape[1]
+    if E > backend.gate_max_experts() or logits.shape[0] == 0:
+        return None
+    ids, l_aux = _TopKWithGShardLoss.apply(logits.contiguous(), min(int(top_k), E), backend)
+    return list(ids.unbind(0)), l_aux
 
 
 GATES = {"top": LinearTopKGate, "cosine_top": CosineTopKGate}

@@ -21,7 +21,7 @@ from ._lib import check, dt, lib, ptr, stream_of
 # (name, start_event, end_event, algorithmic_work, algorithmic_bytes) with CUDA events recorded on the launching stream.
 LAUNCHES = 0
 PROFILE = None
-_KERNELS_PER_CALL = dict(route=3, gather=1, combine=1, esmm=1, estmm=1, ess=2, mask=1)
+_KERNELS_PER_CALL = dict(route=3, gather=1, combine=1, esmm=1, estmm=1, ess=2, mask=1, gate=1)
 
 
 class _Timed:
@@ -226,6 +226,42 @@ def mask_pad_rows(buf: torch.Tensor, r: Routing) -> torch.Tensor:
         check(lib().hexa_mask_pad_rows(ptr(buf), _ld(buf), ptr(r.row_token), ptr(r.pad_offsets), r.num_experts, r.row_capacity,
                                        buf.shape[1], dt(buf), stream_of(buf)), "hexa_mask_pad_rows")
     return buf
+
+
+# -------------------------------------------------------------------------------------------------
+# the step before routing
+# -------------------------------------------------------------------------------------------------
+def gate_max_experts() -> int:
+    return int(lib().hexa_gate_max_experts())
+
+
+def gate_topk(logits: torch.Tensor, top_k: int):
+    """softmax + top-k + GShard loss of float32 logits [T,E] in one kernel.  Returns (ids int32 [k,T] route-major,
+    loss float32 scalar tensor, first_count int32 [E], mass float32 [E])."""
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise L.HexaError("gate_topk: logits must be float32 [T,E] with unit inner stride")
+    T, E = logits.shape
+    dev = logits.device
+    ids = torch.empty(top_k, T, dtype=torch.int32, device=dev)
+    mass = torch.empty(E, dtype=torch.float32, device=dev)
+    cnt = torch.empty(E, dtype=torch.int32, device=dev)
+    loss = torch.empty((), dtype=torch.float32, device=dev)
+    ws = torch.empty(int(lib().hexa_gate_workspace_bytes()), dtype=torch.uint8, device=dev)
+    with _Timed("gate", 2.0 * T * E * 4):
+        check(lib().hexa_gate_topk(ptr(logits), _ld(logits), T, E, top_k, ptr(ids), ptr(mass), ptr(cnt), ptr(loss), ptr(ws),
+                                   ws.numel(), stream_of(logits)), "hexa_gate_topk")
+    return ids, loss, cnt, mass
+
+
+def gate_loss_grad(logits: torch.Tensor, first_count: torch.Tensor, dloss: torch.Tensor) -> torch.Tensor:
+    """Gradient of gate_topk's loss with respect to the logits, scaled by the device scalar dloss."""
+    T, E = logits.shape
+    out = torch.empty(T, E, dtype=torch.float32, device=logits.device)
+    dloss = dloss.detach().to(torch.float32).reshape(1).contiguous()
+    with _Timed("gate", 2.0 * T * E * 4):
+        check(lib().hexa_gate_loss_grad(ptr(logits), _ld(logits), T, E, ptr(first_count), ptr(dloss), ptr(out), _ld(out),
+                                        stream_of(logits)), "hexa_gate_loss_grad")
+    return out
 
 
 # -------------------------------------------------------------------------------------------------

@@ -199,6 +199,27 @@ int hexa_stream_wait_value(const int32_t* addr, int32_t value, void* stream);
 int hexa_mean_slices(const void* local, const void* recv, int n_recv, int64_t elems, int world, void* out, int dtype,
                      void* stream);
 
+/* ---- the step before routing: softmax + top-k + GShard auxiliary loss ---------------------------------------------
+ * Replaces the reference's chain softmax -> torch.topk -> int64 -> int32 casts -> gshard_loss
+ * (hexa_moe_triton/hexa_moe/impls/cascaded_moe.py:568-598, impls/layers.py:480-489, impls/losses.py:12-19) for
+ * float32 logits [num_tokens, num_experts] (leading dimension ld), 1 <= num_experts <= hexa_gate_max_experts().
+ *   ids          int32 [top_k, num_tokens], route-major: ids[j*num_tokens + t] = expert of token t's j-th choice,
+ *                descending score, lowest expert id on ties (what hexa_route reads with stride_k = num_tokens)
+ *   mass         float [num_experts]: column sums of softmax(logits)
+ *   first_count  int32 [num_experts]: tokens whose first choice is the expert
+ *   loss         float [1]: (E/T^2) * sum_e mass_e * first_count_e
+ * All four are overwritten.  workspace: hexa_gate_workspace_bytes() bytes of device memory, contents irrelevant. */
+int hexa_gate_max_experts(void);
+size_t hexa_gate_workspace_bytes(void);
+int hexa_gate_topk(const float* logits, int64_t ld, int64_t num_tokens, int num_experts, int top_k, int32_t* ids,
+                   float* mass, int32_t* first_count, float* loss, void* workspace, size_t workspace_bytes, void* stream);
+
+/* dlogits[t,e] = d loss / d logits[t,e] * dloss[0] for the loss of hexa_gate_topk: the softmax is recomputed from the
+ * logits, first_count is the forward's output, dloss a float in device memory (the upstream gradient).
+ * (What autograd derives for impls/losses.py:12-19 through F.softmax.) */
+int hexa_gate_loss_grad(const float* logits, int64_t ld, int64_t num_tokens, int num_experts, const int32_t* first_count,
+                        const float* dloss, float* dlogits, int64_t ldd, void* stream);
+
 /* Elementwise helper on sorted rows for activations the epilogue does not know:
  * dst[r,:] = row_token[r] >= 0 ? src[r,:] : 0 (restores the zero-pad-row invariant). */
 int hexa_mask_pad_rows(void* buf, int64_t ld, const int32_t* row_token, const int32_t* pad_offsets,

@@ -211,16 +211,18 @@ def test_dense_ffn_on_the_grouped_gemm_kernels(dtype, tokens):
         return [y.detach(), xi.grad] + [params[n_].grad.clone() for n_ in names]
 
     from hexa_moe_b200 import ops
-    before = ops.LAUNCHES
-    got = run()
-    assert ops.LAUNCHES - before >= 9, "the dense depth did not run on this library's kernels"
-    os.environ["HEXA_DENSE_KERNELS"] = "0"
+    os.environ["HEXA_DENSE_MIN_DIM"] = "0"          # by default only model dims >= 512 take the kernel path
     try:
+        before = ops.LAUNCHES
+        got = run()
+        assert ops.LAUNCHES - before >= 9, "the dense depth did not run on this library's kernels"
+        os.environ["HEXA_DENSE_KERNELS"] = "0"
         before = ops.LAUNCHES
         plain = run()
         assert ops.LAUNCHES == before
     finally:
-        del os.environ["HEXA_DENSE_KERNELS"]
+        os.environ.pop("HEXA_DENSE_KERNELS", None)
+        os.environ.pop("HEXA_DENSE_MIN_DIM", None)
     w1, w2, b1, b2 = [params[n_].detach().double().requires_grad_(True) for n_ in names]
     xr = x.double().requires_grad_(True)
     yr = F.gelu(xr @ w1.t() + b1) @ w2 + b2
