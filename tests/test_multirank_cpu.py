@@ -124,3 +124,63 @@ def test_data_centric_two_ranks(proportion):
 @pytest.mark.parametrize("proportion,tokens", [(None, [32, 32]), ([0.3, 0.7], [24, 40])])
 def test_model_centric_two_ranks(proportion, tokens):
     _run(False, proportion, tokens)
+
+
+def _ckpt_worker(rank, world, port, proportion, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from hexa_moe import moe as hmoe
+        E, d, H, L = 4, 16, 64, 2
+        mk = lambda: hmoe.MoE_Cascaded(gate_type={'type': 'top', 'k': 1}, model_dim_list=[d] * L, moe_idx_list=[0, 1],
+                                       mlp_ratio=H // d, mlp_proportion=proportion, num_global_experts=E, total_depth=L,
+                                       data_centric=True, activation_fn=lambda t: F.gelu(t))
+        m = mk()
+        P = _full_params(E, d, H, L, seed=3)
+        src = hmoe.MoE_Buffer([d] * L, E, L, H // d, None, True, True)
+        if rank == 0:                         # only the source rank holds the unsharded checkpoint
+            with torch.no_grad():
+                for i in range(L):
+                    src.batched_fc1_w[i].copy_(P[i]["w1"]); src.batched_fc2_w[i].copy_(P[i]["w2"])
+                    src.batched_fc1_bias[i].copy_(P[i]["b1"]); src.batched_fc2_bias[i].copy_(P[i]["b2"])
+        m.load_ckpt(src, src_rank=0)
+        split = [m.local_dim_list_all[r][0] for r in range(world)]
+        lo, n = sum(split[:rank]), split[rank]
+        for i in range(L):                    # every rank got exactly its slice of the hidden dimension
+            assert torch.equal(m.batched_fc1_w[i].data[:, :n], P[i]["w1"][:, lo: lo + n])
+            assert torch.equal(m.batched_fc2_w[i].data[:, :n], P[i]["w2"][:, lo: lo + n])
+            assert torch.equal(m.batched_fc1_bias[i].data[:, :n], P[i]["b1"][:, lo: lo + n])
+            assert torch.equal(m.batched_fc2_bias[i].data, P[i]["b2"])
+        dst = hmoe.MoE_Buffer([d] * L, E, L, H // d, None, True, True)
+        m.save_ckpt(dst, dst_rank=1)          # gathered back, unevenly sized slices in rank order
+        if rank == 1:
+            for i in range(L):
+                assert torch.equal(dst.batched_fc1_w[i].data, P[i]["w1"])
+                assert torch.equal(dst.batched_fc2_w[i].data, P[i]["w2"])
+                assert torch.equal(dst.batched_fc1_bias[i].data, P[i]["b1"])
+                assert torch.equal(dst.batched_fc2_bias[i].data, P[i]["b2"])
+        q.put((rank, "ok"))
+    except Exception:  # noqa: BLE001
+        import traceback
+        q.put((rank, "FAIL: " + traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("proportion", [None, [0.7, 0.3]])
+def test_checkpoint_scatter_and_gather_two_ranks(proportion):
+    """load_ckpt broadcasts an unsharded MoE_Buffer from one rank and keeps each rank's hidden slice; save_ckpt gathers
+    the (uneven) slices back into an unsharded buffer on another rank (reference cascaded_moe.py:413-525)."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ckpt_worker, args=(r, world, port, proportion, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(60)
+    for rank, msg in res:
+        assert msg == "ok", f"rank {rank}: {msg}"
