@@ -49,6 +49,9 @@ def parse():
                          "captures); small: d=256/H=1024/E=8, 8192 tokens (smoke); c4: the Swin-MoE-B-like network "
                          "(secondary: images/s through the whole synthetic model, 128 images of 192x192 per GPU)")
     ap.add_argument("--images", type=int, default=128, help="c4: images per GPU")
+    ap.add_argument("--mode", default="data", choices=["data", "model"],
+                    help="multi-GPU mode of the layer workloads: data-centric (tokens sharded, expert weights gathered "
+                         "through the pipeline-shared cache) or model-centric (hidden dimension sharded, tokens gathered)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -287,7 +290,7 @@ def main():
     torch.manual_seed(0)
     m = hmoe.MoE_Cascaded(gate_type={'type': 'top', 'k': k, 'fp32_gate': True}, model_dim_list=[d] * L,
                           moe_idx_list=list(range(L)), mlp_ratio=H // d, mlp_proportion=None, num_global_experts=E,
-                          total_depth=L, data_centric=True, mlp_fc1_bias=True, mlp_fc2_bias=True,
+                          total_depth=L, data_centric=args.mode == "data", mlp_fc1_bias=True, mlp_fc2_bias=True,
                           activation_fn=lambda t: F.gelu(t))
     with torch.no_grad():   # random-init weights at a scale that keeps activations O(1)
         for name, p in m.named_parameters():
@@ -403,7 +406,7 @@ def main():
                     warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
                     dtype="bf16", data="synthetic",
                     config=dict(workload=args.workload + "-layer", d_model=d, hidden=H, experts=E,
-                                top_k=k, layers=L, tokens_per_gpu=T, activation="gelu", mode="data-centric",
+                                top_k=k, layers=L, tokens_per_gpu=T, activation="gelu", mode=args.mode + "-centric",
                                 l2="inputs larger than L2 (expert weights %.1f GB per layer)" % (2 * E * H * d * 2 / 1e9)),
                     model_tflops_per_gpu=layer_flops / (ms * 1e-3) / 1e12,
                     e2e=dict(value=e2e_value, unit="tokens/s", ms_per_step=ms_e2e, h2d_bytes_per_step=x_host.numel() * 2,
@@ -412,7 +415,8 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
-        m.dispatch_params.cache.close()      # unmap the other ranks' memory before anyone exits
+        if m.dispatch_params.cache is not None:
+            m.dispatch_params.cache.close()      # unmap the other ranks' memory before anyone exits
         dist.barrier()
         dist.destroy_process_group()
 
