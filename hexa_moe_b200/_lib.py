@@ -39,6 +39,7 @@ SIGNATURES = {
     "hexa_combine_rows": (ci, [vp, i64, vp, i64, ci, i64, vp, i64, ci, vp]),
     "hexa_esmm": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, vp, i64, vp, i64, vp, vp, vp, vp, ci, i64, i64, i64, ci, ci, ci, ci, vp]),
     "hexa_estmm": (ci, [vp, i64, vp, i64, vp, ci, i64, i64, i64, vp, i64, i64, i64, i64, ci, ci, ci, ci, vp]),
+    "hexa_estmm_scatter": (ci, [vp, i64, vp, i64, vp, ci, i64, i64, i64, vp, ci, i64, i64, i64, ci, ci, vp]),
     "hexa_copy_2d": (ci, [vp, i64, vp, i64, i64, i64, vp]),
     "hexa_stream_wait_value": (ci, [vp, C.c_int32, vp]),
     "hexa_mean_slices": (ci, [vp, vp, ci, i64, ci, vp, ci, vp]),

@@ -17,5 +17,5 @@ int esmm_tc_launch(const void*, int64_t, const void*, int, int64_t, int64_t, con
                    int, int, cudaStream_t);
 bool estmm_tc_supported(const void*, int64_t, const void*, int64_t, const void*, int64_t, int64_t, int64_t, int64_t, int, int);
 int estmm_tc_launch(const void*, int64_t, const void*, int64_t, const int32_t*, int, int64_t, int64_t, int64_t, void*, int64_t,
-                    int64_t, int64_t, int64_t, int, int, int, cudaStream_t);
+                    int64_t, int64_t, int64_t, int, int, int, cudaStream_t, void* const* split_out = nullptr, int n_split = 0);
 }  // namespace hexa

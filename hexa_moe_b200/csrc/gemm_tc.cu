@@ -61,6 +61,8 @@ struct Params {
   int64_t ldc;
   int64_t c_estride;  // ESTMM only
   int64_t m_split, split_stride;  // ESTMM: output row m lives at (m / m_split) * split_stride + (m % m_split) * ldc
+  void* c_split[16];  // ESTMM, n_split > 0: slice m / m_split of the output goes to this base instead (it may be
+  int n_split;        // another GPU's memory: the reduce-scatter layout written straight into the owners' buffers)
   int64_t n;        // output columns
   int64_t k;        // ESMM: contraction length ; ESTMM: unused
   int64_t m;        // ESTMM: output rows per expert
@@ -590,7 +592,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int64_t mrow = (int64_t)tile.m0 + rloc;
           if (mrow < p.m) {
             if (p.out_f32) {
-              float* o = reinterpret_cast<float*>(p.c) + (int64_t)tile.e * p.c_estride + (mrow / p.m_split) * p.split_stride + (mrow % p.m_split) * p.ldc + gcol;
+              float* o = (p.n_split ? reinterpret_cast<float*>(p.c_split[mrow / p.m_split])
+                                    : reinterpret_cast<float*>(p.c) + (mrow / p.m_split) * p.split_stride) +
+                         (int64_t)tile.e * p.c_estride + (mrow % p.m_split) * p.ldc + gcol;
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
                 if (gcol + g * 4 < p.n) {
@@ -604,7 +608,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
               }
             } else {
-              uint16_t* o = reinterpret_cast<uint16_t*>(p.c) + (int64_t)tile.e * p.c_estride + (mrow / p.m_split) * p.split_stride + (mrow % p.m_split) * p.ldc + gcol;
+              uint16_t* o = (p.n_split ? reinterpret_cast<uint16_t*>(p.c_split[mrow / p.m_split])
+                                       : reinterpret_cast<uint16_t*>(p.c) + (mrow / p.m_split) * p.split_stride) +
+                            (int64_t)tile.e * p.c_estride + (mrow % p.m_split) * p.ldc + gcol;
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
                 if (gcol + g * 8 < p.n) {
@@ -892,7 +898,8 @@ bool estmm_tc_supported(const void* p, int64_t ldp, const void* q, int64_t ldq, 
 
 int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets, int E,
                     int64_t row_cap, int64_t m, int64_t n, void* out, int64_t ldo, int64_t o_estride, int64_t m_split,
-                    int64_t split_stride, int dtype, int out_dtype, int beta, cudaStream_t stream) {
+                    int64_t split_stride, int dtype, int out_dtype, int beta, cudaStream_t stream, void* const* split_out,
+                    int n_split) {
   const int is_bf16 = dtype == HEXA_BF16;
   const int BN = n > 128 ? 256 : 128;
   const int ctas = (BN == 256 && m > BLOCK_M && pairs_enabled()) ? 2 : 1;
@@ -916,6 +923,8 @@ int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, con
   Params p{};
   p.pad_offsets = pad_offsets; p.c = out; p.ldc = ldo; p.c_estride = o_estride; p.n = n; p.m = m; p.E = E;
   p.m_split = m_split; p.split_stride = split_stride;
+  p.n_split = n_split;
+  for (int i = 0; i < n_split && i < 16; ++i) p.c_split[i] = split_out[i];
   p.is_bf16 = is_bf16; p.out_f32 = out_dtype == HEXA_F32; p.beta = beta;
   p.status = status_word(); p.debug = debug_flags();
   const int64_t max_tiles = (int64_t)E * ceil_div(m, BLOCK_M * ctas) * ceil_div(n, BN);

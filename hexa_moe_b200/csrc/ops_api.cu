@@ -60,6 +60,29 @@ extern "C" int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq
                            stream);
 }
 
+extern "C" int hexa_estmm_scatter(const void* p, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets, int E,
+                                  int64_t row_cap, int64_t m, int64_t n, void* const* split_out, int n_split, int64_t ldo,
+                                  int64_t o_estride, int64_t m_split, int dtype, int out_dtype, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  HEXA_REQUIRE(p && q && split_out && pad_offsets, "hexa_estmm_scatter: null pointer");
+  HEXA_REQUIRE(E > 0 && row_cap >= 0 && row_cap % kRowTile == 0 && m > 0 && n > 0,
+               "hexa_estmm_scatter: bad sizes (row_capacity must be a multiple of %d)", kRowTile);
+  HEXA_REQUIRE(m_split > 0 && n_split >= 1 && n_split <= 16 && (int64_t)n_split * m_split >= m && (int64_t)(n_split - 1) * m_split < m,
+               "hexa_estmm_scatter: needs 1 <= n_split <= 16 slices of m_split rows covering m");
+  HEXA_REQUIRE(ldp >= m && ldq >= n && ldo >= n && o_estride >= (m_split - 1) * ldo + n, "hexa_estmm_scatter: leading dimension too small");
+  HEXA_REQUIRE(dtype == HEXA_F16 || dtype == HEXA_BF16, "hexa_estmm_scatter: 16-bit inputs only");
+  HEXA_REQUIRE(out_dtype == HEXA_F32 || out_dtype == dtype, "hexa_estmm_scatter: out_dtype must be fp32 or the input dtype");
+  for (int i = 0; i < n_split; ++i) {
+    HEXA_REQUIRE(split_out[i], "hexa_estmm_scatter: split_out[%d] is null", i);
+    if (!estmm_tc_supported(p, ldp, q, ldq, split_out[i], ldo, o_estride, 0, n, dtype, out_dtype)) {
+      set_error("hexa_estmm_scatter: needs 16-byte aligned pointers and leading dimensions / n that are multiples of 8");
+      return HEXA_ERR_UNSUPPORTED;
+    }
+  }
+  return estmm_tc_launch(p, ldp, q, ldq, pad_offsets, E, row_cap, m, n, split_out[0], ldo, o_estride, m_split, 0, dtype, out_dtype, 0,
+                         stream, split_out, n_split);
+}
+
 extern "C" int hexa_copy_2d(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes, int64_t width_bytes,
                             int64_t height, void* stream_) {
   HEXA_REQUIRE(dst && src, "hexa_copy_2d: null pointer");

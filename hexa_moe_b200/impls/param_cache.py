@@ -256,7 +256,7 @@ class PipelineSharedCache:
             red = dict(
                 grad=dict(fc1=[torch.empty(n1, device=dev, dtype=dtype) for _ in range(2)],
                           fc2=[torch.empty(n2, device=dev, dtype=dtype) for _ in range(2)]),
-                recv=torch.empty(max(n1, n2) // W * max(W - 1, 1), device=dev, dtype=dtype),
+                recv=None, recv_elems=max(n1, n2) // W * max(W - 1, 1),     # staging of the copy-engine variant, on demand
                 flags=torch.zeros(W, device=dev, dtype=torch.int32),
                 seq_table=torch.arange(1, (1 << 16) + 1, device=dev, dtype=torch.int32), seq=0, seq_base=0, old_tables=[],
                 free={("fc1", 0): None, ("fc1", 1): None, ("fc2", 0): None, ("fc2", 1): None})
@@ -323,6 +323,8 @@ class PipelineSharedCache:
         n = out.numel()
         par = stage % 2
         self._peer_barrier()                                      # every rank's gradient is complete
+        if red["recv"] is None:      # allocated on the side stream, the only stream that uses it
+            red["recv"] = torch.empty(red["recv_elems"], device=out.device, dtype=out.dtype)
         recv = red["recv"][: (W - 1) * n].view(W - 1, n)
         i = 0
         for k in range(1, W):

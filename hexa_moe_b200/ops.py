@@ -157,15 +157,34 @@ def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Opti
 
 
 def estmm(p: torch.Tensor, q: torch.Tensor, r: Routing, out_dtype: Optional[torch.dtype] = None,
-          out: Optional[torch.Tensor] = None, beta: int = 0, engine: int = L.ENGINE_AUTO, ranks: int = 1) -> torch.Tensor:
+          out=None, beta: int = 0, engine: int = L.ENGINE_AUTO, ranks: int = 1):
     """out[e] = p_e^T q_e over expert e's rows: [E, p.cols, q.cols].
     ranks > 1 (p.cols divisible by it): the result is laid out [ranks, E, p.cols/ranks, q.cols], i.e. already
-    grouped by the rank that owns each slice of the hidden dimension (what a reduce-scatter consumes)."""
+    grouped by the rank that owns each slice of the hidden dimension (what a reduce-scatter consumes).  `out` may
+    then also be a list of `ranks` tensors [E, p.cols/ranks, q.cols] in this GPU's memory, one per owner: each slice
+    is stored straight into its tensor (hexa_estmm_scatter); the list is returned."""
     if r.align % L.ROW_TILE:
         raise L.HexaError("estmm: routing must be aligned to 128 rows")
     m, n = p.shape[1], q.shape[1]
     if p.dtype != q.dtype:
         raise L.HexaError("estmm: p and q dtypes differ")
+    rows_ = r.num_tokens * r.top_k
+    if isinstance(out, (list, tuple)):
+        if ranks != len(out) or m % ranks or beta:
+            raise L.HexaError("estmm: a list of outputs needs ranks == len(out), divisible rows and beta = 0")
+        o0 = out[0]
+        for t in out:
+            if t.shape != o0.shape or t.dtype != o0.dtype or t.stride() != o0.stride() or t.stride(-1) != 1:
+                raise L.HexaError("estmm: the per-owner outputs must agree in shape, dtype and strides")
+        if tuple(o0.shape) != (r.num_experts, m // ranks, n):
+            raise L.HexaError("estmm: per-owner outputs must be [E, rows/ranks, cols]")
+        import ctypes as C
+        ptrs = (C.c_void_p * ranks)(*[t.data_ptr() for t in out])
+        with _Timed("estmm", 2.0 * rows_ * m * n, float(p.element_size() * rows_ * (m + n) + o0.element_size() * r.num_experts * m * n)):
+            check(lib().hexa_estmm_scatter(ptr(p), _ld(p), ptr(q), _ld(q), ptr(r.pad_offsets), r.num_experts, r.row_capacity, m, n,
+                                           ptrs, ranks, o0.stride(1), o0.stride(0), m // ranks, dt(p), dt(o0), stream_of(p)),
+                  "hexa_estmm_scatter")
+        return out
     if ranks > 1:
         if m % ranks:
             raise L.HexaError("estmm: the row count must be divisible by ranks")
@@ -180,7 +199,6 @@ def estmm(p: torch.Tensor, q: torch.Tensor, r: Routing, out_dtype: Optional[torc
         ldo, estride, m_split, split_stride = out.stride(1), out.stride(0), 0, 0
     if out.stride(-1) != 1:
         raise L.HexaError("estmm: out must have unit inner stride")
-    rows_ = r.num_tokens * r.top_k
     with _Timed("estmm", 2.0 * rows_ * m * n, float(p.element_size() * rows_ * (m + n) + out.element_size() * r.num_experts * m * n)):
         check(lib().hexa_estmm(ptr(p), _ld(p), ptr(q), _ld(q), ptr(r.pad_offsets), r.num_experts, r.row_capacity, m, n, ptr(out),
                                ldo, estride, m_split, split_stride, dt(p), dt(out), beta, engine, stream_of(p)), "hexa_estmm")

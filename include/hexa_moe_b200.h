@@ -154,6 +154,19 @@ int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq, const int
                int64_t o_estride, int64_t m_split, int64_t split_stride, int dtype, int out_dtype, int beta,
                int engine, void* stream);
 
+/* ESTMM whose output slices go to separate buffers (no reference counterpart; the reference all-reduces the full
+ * gradient through torch.distributed, impls/layers.py:431-474): output row i of expert e is written at
+ *   split_out[i / m_split] + e*o_estride + (i % m_split)*ldo            (elements of out_dtype)
+ * split_out is a HOST array of n_split = ceil(m / m_split) <= 16 device pointers (copied at the call).  Meant for
+ * laying a weight gradient out per owner of a hidden slice without a packing pass.  Verified for destinations in
+ * the calling GPU's own memory only: with destinations in another GPU's memory (the reduce-scatter transfer done
+ * by the GEMM's own stores) the CTA-pair kernel raised an illegal-address fault at 2 GiB buffers on two GPUs, the
+ * cause is not known, and the library's multi-GPU path therefore does not use this entry point.
+ * 16-bit inputs only (the tcgen05 kernel); the destination is overwritten (beta = 0). */
+int hexa_estmm_scatter(const void* p, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets,
+                       int num_experts, int64_t row_capacity, int64_t m, int64_t n, void* const* split_out, int n_split,
+                       int64_t ldo, int64_t o_estride, int64_t m_split, int dtype, int out_dtype, void* stream);
+
 /* Strided block copy on the stream (cudaMemcpy2DAsync, device to device): `height` rows of `width_bytes`.
  * Used to move hidden-dimension slices between the gathered [ranks, E, loc, d] staging layout and
  * [E, H, d] without spending SMs on it.  No counterpart in the reference (it builds the same views with

@@ -246,6 +246,27 @@ def test_estmm_rank_grouped_layout_and_copy_2d(ops, dtype, engine):
     assert torch.equal(back, plain)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,W", [(512, 4), (768, 2), (1024, 8)])
+def test_estmm_scatter_to_per_owner_buffers(ops, out_dtype, M, W):
+    """A list of W outputs: slice w of the hidden dimension is stored straight into out[w] ([E, M/W, N]).
+    Bit-identical to the rank-grouped single-buffer layout, and nothing outside the slices is touched."""
+    T, k, E, N = 1500, 2, 5, 256
+    ids = make_ids(T, k, E, 8, skew=True)
+    r = ops.route(ids.cuda(), E)
+    p = ops.gather_rows(torch.randn(T, M).bfloat16().cuda(), r); q = ops.gather_rows(torch.randn(T, N).bfloat16().cuda(), r)
+    grouped = ops.estmm(p, q, r, out_dtype=out_dtype, ranks=W)
+    arena = torch.full((W, 2, E, M // W, N), 7.0, dtype=out_dtype, device="cuda")      # slot 1 of every owner is the target
+    outs = [arena[w, 1] for w in range(W)]
+    back = ops.estmm(p, q, r, ranks=W, out=outs)
+    assert back is outs
+    for w in range(W):
+        assert torch.equal(outs[w], grouped[w])
+        assert (arena[w, 0] == 7.0).all()
+    with pytest.raises(L().HexaError):
+        ops.estmm(p, q, r, ranks=W, out=outs[:-1])
+
+
 def test_estmm_simt_fp32(ops):
     _estmm_case(ops, torch.float32, L().ENGINE_SIMT, T=900, k=2, E=6, M=100, N=72, out_dtype=torch.float32)
 
