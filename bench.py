@@ -13,8 +13,9 @@ mode (tokens sharded over ranks, expert weights sharded along the hidden dimensi
 per layer and their gradients reduce-scattered): weak scaling.
 
 Prints ONE JSON line (rank 0).  `value` is measured with inputs resident in HBM; `e2e` repeats the
-measurement with the step's input copied from pinned host memory and the loss read back to the
-host inside the timed region.  `roofline` is for the dominant kernel (the tcgen05 grouped GEMM),
+measurement with each step's input copied from pinned host memory (double-buffered: the upload of
+step i+1 runs on a copy stream while step i computes, one upload per timed step) and the loss read
+back to the host inside the timed region.  `roofline` is for the dominant kernel (the tcgen05 grouped GEMM),
 from CUDA events recorded around its launches during the timed steps.  `cpu_baseline` times the
 CPU oracle's restatement of the same layer on the host cores on a bounded sample.
 """
@@ -62,6 +63,37 @@ def peaks():
         p = json.load(open(path))
         return dict(tflops=float(p.get("bf16_tflops_sustained", p.get("bf16_tflops"))), hbm=float(p["hbm_gbs"]), source="measured")
     return dict(tflops=1400.0, hbm=6650.0, source="fallback")
+
+
+class InputPrefetcher:
+    """Double-buffered host -> device feed for the end-to-end measurement: every call of next() returns the device
+    buffer whose upload (from pinned host memory, on a copy stream) was started one step earlier and starts the
+    upload of the following step's input into the other buffer, so each timed step contains exactly one upload,
+    overlapped with the previous step's kernels."""
+
+    def __init__(self, host, bufs):
+        import torch
+        self.torch, self.host, self.bufs = torch, host, bufs
+        self.stream = torch.cuda.Stream(device=bufs[0].device)
+        self.ready = [None, None]
+        self.i = 0
+        self._upload(0)
+
+    def _upload(self, slot):
+        torch = self.torch
+        self.stream.wait_stream(torch.cuda.current_stream())      # the buffer's previous consumer has been enqueued
+        with torch.cuda.stream(self.stream):
+            self.bufs[slot].copy_(self.host, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        self.ready[slot] = ev
+
+    def next(self):
+        slot = self.i & 1
+        self.i += 1
+        self.torch.cuda.current_stream().wait_event(self.ready[slot])
+        self._upload(slot ^ 1)
+        return self.bufs[slot]
 
 
 class ClockSampler:
@@ -197,9 +229,10 @@ def run_swin(args, dev, rank, world, timed_factory=None):
         loss.backward()
         return loss
 
+    loader = InputPrefetcher(imgs_host, [stage, torch.empty_like(imgs_dev)])
+
     def step_e2e():
-        stage.copy_(imgs_host, non_blocking=True)
-        loss = step(stage)
+        loss = step(loader.next())
         loss_host.copy_(loss.detach(), non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -326,9 +359,13 @@ def main():
     def step_resident():
         return step(x_dev)
 
+    loader = InputPrefetcher(x_host, [x_stage, torch.empty_like(x_dev)])
+
     def step_e2e():
-        x_stage.copy_(x_host, non_blocking=True)
-        loss = step(x_stage)
+        # the way a training loop feeds the module: this step's input was uploaded (pinned host -> device, on a copy
+        # stream) while the previous step computed; the upload of the next one starts now; the loss is read back
+        x = loader.next()
+        loss = step(x)
         loss_host.copy_(loss.detach(), non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return float(loss_host)
