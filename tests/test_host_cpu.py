@@ -135,3 +135,27 @@ def test_checkpoint_buffer_roundtrip_single_rank():
     for i in range(2):
         assert torch.equal(m2.batched_fc1_w[i], m.batched_fc1_w[i]) and torch.equal(m2.batched_fc2_bias[i], m.batched_fc2_bias[i])
         assert torch.equal(m2.batched_fc1_bias[i], m.batched_fc1_bias[i])
+
+
+def test_split_terms_reproduce_fp32_exactly():
+    """The fp32 gate weight is fed to the tensor cores as three bf16 terms; their sum must be the fp32 value itself
+    (24 mantissa bits = 3 x 8), otherwise the 'fp32 gate' would silently lose precision."""
+    from hexa_moe_b200.impls.gating import _split_terms
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(64, 300, generator=g) * torch.logspace(-6, 3, 300)
+    terms = _split_terms(w, torch.bfloat16, 3)
+    assert all(t.dtype == torch.bfloat16 for t in terms)
+    total = (terms[0].double() + terms[1].double()) + terms[2].double()
+    assert torch.equal(total.float(), w)
+    two = terms[0].double() + terms[1].double()                 # two terms are not enough: that is why there are three
+    assert not torch.equal(two.float(), w)
+
+
+def test_fused_gate_step_declines_what_it_cannot_do():
+    """CPU logits, half-precision logits and a missing backend fall through to the PyTorch chain (None)."""
+    from hexa_moe_b200.impls.gating import fused_topk_gshard
+    from hexa_moe_b200 import ops
+    logits = torch.randn(16, 8)
+    assert fused_topk_gshard(logits, 2, ops) is None
+    assert fused_topk_gshard(logits.to(torch.bfloat16), 2, ops) is None
+    assert fused_topk_gshard(logits, 2, None) is None
