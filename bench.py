@@ -180,6 +180,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if args.workload not in WORKLOADS:      # the Swin harness is stock PyTorch around the layer; only the layer has a CPU arm
+        print(json.dumps(dict(impl="reference", unavailable="no CPU arm for workload %s: use one of %s"
+                                                            % (args.workload, ", ".join(WORKLOADS)))), flush=True)
+        return
     d, H, EXPERTS, _ = WORKLOADS[args.workload]
     k = TOP_K
     E_s = 8
