@@ -53,6 +53,10 @@ def parse():
     ap.add_argument("--mode", default="data", choices=["data", "model"],
                     help="multi-GPU mode of the layer workloads: data-centric (tokens sharded, expert weights gathered "
                          "through the pipeline-shared cache) or model-centric (hidden dimension sharded, tokens gathered)")
+    ap.add_argument("--hetero", action="store_true",
+                    help="the heterogeneous model-centric case: hidden dimension split 0.2/0.2/0.15/0.15/0.1/0.1/0.05/0.05 "
+                         "over 8 ranks (neighbouring shares merged for 4 and 2 ranks), 131072 tokens in total (strong "
+                         "scaling), implies --mode model")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -324,9 +328,18 @@ def main():
     d, H, E, T_default = WORKLOADS[args.workload]
     k, L = TOP_K, LAYERS
     T = args.tokens or T_default
+    proportion = None
+    if args.hetero:
+        if 8 % world:
+            raise SystemExit("--hetero needs 1, 2, 4 or 8 ranks")
+        args.mode = "model"
+        eighth = [0.2, 0.2, 0.15, 0.15, 0.1, 0.1, 0.05, 0.05]
+        g = 8 // world
+        proportion = [round(sum(eighth[i * g:(i + 1) * g]), 6) for i in range(world)]
+        T = (args.tokens or T_default) // world            # the token count is global: every rank contributes its share
     torch.manual_seed(0)
     m = hmoe.MoE_Cascaded(gate_type={'type': 'top', 'k': k, 'fp32_gate': True}, model_dim_list=[d] * L,
-                          moe_idx_list=list(range(L)), mlp_ratio=H // d, mlp_proportion=None, num_global_experts=E,
+                          moe_idx_list=list(range(L)), mlp_ratio=H // d, mlp_proportion=proportion, num_global_experts=E,
                           total_depth=L, data_centric=args.mode == "data", mlp_fc1_bias=True, mlp_fc2_bias=True,
                           activation_fn=lambda t: F.gelu(t))
     with torch.no_grad():   # random-init weights at a scale that keeps activations O(1)
@@ -444,9 +457,9 @@ def main():
                             sample=f"{n_s} tokens top-{k} over 8 of the {E} experts (same d, hidden and per-token work), fp32, one pass")
     if rank == 0:
         line = dict(metric="moe_layer_fwd_bwd_tokens_per_s", value=value, unit="tokens/s", n_gpus=n_gpus, steps=args.steps,
-                    warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
-                    dtype="bf16", data="synthetic",
-                    config=dict(workload=args.workload + "-layer", d_model=d, hidden=H, experts=E,
+                    warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True,
+                    scaling="strong" if args.hetero else "weak", vs_baseline=None, dtype="bf16", data="synthetic",
+                    config=dict(workload=args.workload + "-layer", d_model=d, hidden=H, experts=E, hidden_split=proportion,
                                 top_k=k, layers=L, tokens_per_gpu=T, activation="gelu", mode=args.mode + "-centric",
                                 l2="inputs larger than L2 (expert weights %.1f GB per layer)" % (2 * E * H * d * 2 / 1e9)),
                     model_tflops_per_gpu=layer_flops / (ms * 1e-3) / 1e12,

@@ -817,7 +817,12 @@ bool esmm_tc_supported(const void* a, int64_t lda, const void* b, int64_t ldb, i
                        int dtype) {
   if (dtype != HEXA_F16 && dtype != HEXA_BF16) return false;
   if (!aligned16(a) || !aligned16(b) || !aligned16(c) || (aux && !aligned16(aux)) || (bias && !aligned16(bias))) return false;
-  if (lda % 8 || ldb % 8 || b_estride % 8 || ldc % 8 || (aux && ldaux % 8) || (bias && ldbias % 4) || n_out % 8) return false;
+  if (lda % 8 || ldb % 8 || b_estride % 8 || ldc % 8 || (aux && ldaux % 8) || (bias && ldbias % 4)) return false;
+  // n_out itself may be any size (a rank's slice of an unevenly split hidden dimension): the TMA stores clip at
+  // n_out, but the epilogue's 16-byte reads of bias and saved pre-activation run to the end of the last chunk, so
+  // those rows must be padded to whole chunks
+  const int64_t n8 = (n_out + 7) / 8 * 8, n4 = (n_out + 3) / 4 * 4;
+  if ((aux && ldaux < n8) || (bias && ldbias < n4)) return false;
   return true;
 }
 

@@ -94,6 +94,15 @@ def route(ids: torch.Tensor, num_experts: int, align: int = L.ROW_TILE, route_ma
     return r
 
 
+def sorted_buffer(rows: int, cols: int, dtype, device) -> torch.Tensor:
+    """[rows, cols] buffer whose row pitch is a multiple of 16 bytes (8 elements), as the TMA-fed GEMMs need; for a
+    column count that is not (a rank's slice of an unevenly split hidden dimension) it is a view of a wider one."""
+    pitch = (cols + 7) // 8 * 8
+    if pitch == cols:
+        return torch.empty(rows, cols, dtype=dtype, device=device)
+    return torch.empty(rows, pitch, dtype=dtype, device=device)[:, :cols]
+
+
 def _ld(t: torch.Tensor) -> int:
     if t.dim() != 2 or t.stride(1) != 1:
         raise L.HexaError("expected a 2-D tensor with unit inner stride")
@@ -104,7 +113,7 @@ def gather_rows(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = Non
     """Token order -> sorted rows: out[row] = src[row_token[row]] (zeros for pad rows)."""
     cols = src.shape[1]
     if out is None:
-        out = torch.empty(r.row_capacity, cols, dtype=src.dtype, device=src.device)
+        out = sorted_buffer(r.row_capacity, cols, src.dtype, src.device)
     with _Timed("gather", 2.0 * r.num_tokens * r.top_k * cols * src.element_size()):
         check(lib().hexa_gather_rows(ptr(src), _ld(src), ptr(r.row_token), ptr(r.pad_offsets), r.num_experts, r.row_capacity,
                                      cols, ptr(out), _ld(out), dt(src), stream_of(src)), "hexa_gather_rows")
@@ -143,7 +152,7 @@ def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Opti
     if bias is not None and bias.dtype != torch.float32:
         raise L.HexaError("esmm: bias must be float32")
     if out is None:
-        out = torch.empty(r.row_capacity, n_out, dtype=a.dtype, device=a.device)
+        out = sorted_buffer(r.row_capacity, n_out, a.dtype, a.device)
     rows_ = r.num_tokens * r.top_k
     es_ = a.element_size()
     nbytes = es_ * (rows_ * k + r.num_experts * n_out * k + rows_ * n_out * (1 if epilogue == L.EPI_LINEAR else 2))
@@ -296,7 +305,16 @@ class LayerState:
 
 
 def _f32(t):
-    return None if t is None else t.detach().to(torch.float32).contiguous()
+    """Bias as the fp32 [E, n] operand of the epilogue; rows padded to whole 16-byte chunks when n is not one."""
+    if t is None:
+        return None
+    t = t.detach()
+    n = t.shape[-1]
+    if n % 4 == 0:
+        return t.to(torch.float32).contiguous()
+    out = torch.zeros(*t.shape[:-1], (n + 3) // 4 * 4, dtype=torch.float32, device=t.device)
+    out[..., :n] = t
+    return out[..., :n]
 
 
 def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=False, engine=L.ENGINE_AUTO,
@@ -311,7 +329,7 @@ def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=Fa
     xs = gather_rows(x, r)
     b1f, b2f = _f32(b1), _f32(b2)
     H = w1.shape[1]
-    y1 = torch.empty(r.row_capacity, H, dtype=x.dtype, device=x.device)
+    y1 = sorted_buffer(r.row_capacity, H, x.dtype, x.device)
     g = None
     if act_id >= 0:
         h = esmm(xs, w1, L.B_NK, r, b1f, L.EPI_ACT, act_id, aux=y1, engine=engine)
@@ -322,9 +340,9 @@ def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=Fa
                 yy = y1.detach().requires_grad_(True)
                 hh = act_fn(yy)
                 (g,) = torch.autograd.grad(hh.sum(), yy)
-            h = hh.detach().contiguous()
+            h = sorted_buffer(r.row_capacity, H, x.dtype, x.device).copy_(hh.detach())
         else:
-            h = act_fn(y1).contiguous()
+            h = sorted_buffer(r.row_capacity, H, x.dtype, x.device).copy_(act_fn(y1))
         mask_pad_rows(h, r)
     if before_fc2 is not None:      # e.g. wait for w2 to finish arriving from the other ranks
         before_fc2()
@@ -407,10 +425,10 @@ def dense_forward(x, w1, w2, b1, b2, act_id: int, need_state=True, engine=L.ENGI
     T = x.shape[0]
     r = dense_routing(T, x.device)
     xs = _dense_rows(x, r)
-    y1 = torch.empty(r.row_capacity, w1.shape[0], dtype=x.dtype, device=x.device)
-    h = esmm(xs, w1.unsqueeze(0), L.B_NK, r, None if b1 is None else _f32(b1).view(1, -1), L.EPI_ACT, act_id, aux=y1,
+    y1 = sorted_buffer(r.row_capacity, w1.shape[0], x.dtype, x.device)
+    h = esmm(xs, w1.unsqueeze(0), L.B_NK, r, None if b1 is None else _f32(b1).unsqueeze(0), L.EPI_ACT, act_id, aux=y1,
              engine=engine)
-    ys = esmm(h, w2.unsqueeze(0), L.B_KN, r, None if b2 is None else _f32(b2).view(1, -1), L.EPI_LINEAR, engine=engine)
+    ys = esmm(h, w2.unsqueeze(0), L.B_KN, r, None if b2 is None else _f32(b2).unsqueeze(0), L.EPI_LINEAR, engine=engine)
     return ys[:T], (LayerState(r, xs, y1, h, None) if need_state else None)
 
 

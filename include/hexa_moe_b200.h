@@ -130,7 +130,12 @@ int hexa_combine_rows(const void* src, int64_t src_ld, const int32_t* token_row,
  * bias fp32 [E, n_out] (ldbias) or NULL, b expert stride b_estride and row stride ldb in elements.
  * Rows with row_token[r] < 0 are written as zeros.  Segments must be aligned to 128 rows.
  * pair_block: the list hexa_route produced, or NULL; with it (and n_out > 128, 16-bit data) the tcgen05 kernel
- * runs on clusters of two CTAs (256-row tiles, each CTA loading half of the weight tile). */
+ * runs on clusters of two CTAs (256-row tiles, each CTA loading half of the weight tile).
+ * The tcgen05 kernel takes 16-bit data with 16-byte aligned pointers and lda, ldb, b_estride, ldc, ldaux multiples
+ * of 8 elements, ldbias a multiple of 4; n_out and k themselves may be any size (a rank's slice of an unevenly split
+ * hidden dimension) as long as aux rows are padded to a multiple of 8 elements and bias rows to a multiple of 4
+ * (ldaux >= roundup(n_out, 8), ldbias >= roundup(n_out, 4)): the epilogue reads them in 16-byte chunks.  Anything
+ * else runs on the CUDA-core kernel under HEXA_ENGINE_AUTO and is refused under HEXA_ENGINE_TCGEN05. */
 int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
               const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
               const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,

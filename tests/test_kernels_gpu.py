@@ -134,16 +134,17 @@ def _esmm_case(ops, dtype, engine, T, k, E, K, N, b_layout, epilogue, act, seed=
     b = torch.randn(E, N, generator=g) if bias else None
     wdev = (w.transpose(1, 2).contiguous() if b_layout == Lb.B_NK else w).cuda()
     xs = ops.gather_rows(x.cuda(), r)
+    bdev = None if b is None else ops._f32(b.cuda())            # rows padded to whole 16-byte chunks when N % 4 != 0
     aux_pre = None
     if epilogue == Lb.EPI_DACT:
         pre = torch.randn(T, N, generator=g).to(dtype)
         aux_pre = ops.gather_rows(pre.cuda(), r)
-        out = ops.esmm(xs, wdev, b_layout, r, None if b is None else b.cuda(), epilogue, act, aux=aux_pre, engine=engine)
+        out = ops.esmm(xs, wdev, b_layout, r, bdev, epilogue, act, aux=aux_pre, engine=engine)
     elif epilogue == Lb.EPI_ACT:
-        aux_pre = torch.empty(r.row_capacity, N, dtype=dtype, device="cuda")
-        out = ops.esmm(xs, wdev, b_layout, r, None if b is None else b.cuda(), epilogue, act, aux=aux_pre, engine=engine)
+        aux_pre = ops.sorted_buffer(r.row_capacity, N, dtype, "cuda")
+        out = ops.esmm(xs, wdev, b_layout, r, bdev, epilogue, act, aux=aux_pre, engine=engine)
     else:
-        out = ops.esmm(xs, wdev, b_layout, r, None if b is None else b.cuda(), epilogue, act, engine=engine)
+        out = ops.esmm(xs, wdev, b_layout, r, bdev, epilogue, act, engine=engine)
     torch_act = {Lb.ACT_NONE: lambda t: t, Lb.ACT_RELU: F.relu, Lb.ACT_GELU: F.gelu,
                  Lb.ACT_GELU_TANH: lambda t: F.gelu(t, approximate="tanh"), Lb.ACT_SILU: F.silu}[act]
     n_pad = int(r.pad_offsets[-1])
@@ -183,6 +184,15 @@ def test_esmm_tcgen05_linear(ops, dtype, b_layout):
 def test_esmm_tcgen05_ragged_dims(ops, b_layout, K, N):
     """K not a multiple of 64 (TMA zero fill), N not a multiple of the tile, both tile widths."""
     _esmm_case(ops, torch.bfloat16, L().ENGINE_TCGEN05, T=900, k=2, E=4, K=K, N=N, b_layout=b_layout, epilogue=0, act=0, seed=2)
+
+
+@pytest.mark.parametrize("b_layout,K,N,epilogue", [(0, 128, 203, 0), (0, 128, 203, 1), (0, 256, 1639, 2), (1, 203, 128, 0),
+                                                   (1, 1639, 256, 0), (0, 64, 1229, 1)])
+def test_esmm_tcgen05_odd_widths(ops, b_layout, K, N, epilogue):
+    """Output widths and contraction lengths that are not multiples of 8: a rank's slice of an unevenly split hidden
+    dimension (8192 x 0.2 = 1639 columns).  The buffers keep a 16-byte row pitch, the tensor cores do the work."""
+    _esmm_case(ops, torch.bfloat16, L().ENGINE_TCGEN05, T=700, k=2, E=3, K=K, N=N, b_layout=b_layout, epilogue=epilogue,
+               act=2 if epilogue else 0, seed=6)
 
 
 @pytest.mark.parametrize("epilogue,act", [(1, 2), (2, 2), (1, 1), (2, 1), (1, 4), (2, 3)])
@@ -279,7 +289,9 @@ def test_estmm_tcgen05(ops, dtype, out_dtype, M, N):
 
 
 @pytest.mark.parametrize("dtype,E,k,d,H,act", [(torch.float32, 8, 1, 128, 512, "gelu"), (torch.bfloat16, 8, 2, 256, 1024, "gelu"),
-                                               (torch.float16, 5, 2, 128, 320, "relu"), (torch.bfloat16, 4, 2, 128, 256, "generic")])
+                                               (torch.float16, 5, 2, 128, 320, "relu"), (torch.bfloat16, 4, 2, 128, 256, "generic"),
+                                               (torch.bfloat16, 4, 2, 128, 203, "gelu"), (torch.bfloat16, 3, 1, 256, 1639, "gelu"),
+                                               (torch.bfloat16, 4, 2, 128, 203, "generic")])
 def test_layer_forward_backward(ops, dtype, E, k, d, H, act):
     Lb = L()
     T = 1200
@@ -292,8 +304,11 @@ def test_layer_forward_backward(ops, dtype, E, k, d, H, act):
     dy = torch.randn(T, d, generator=g).to(dtype)
     fn = {"gelu": F.gelu, "relu": F.relu, "generic": lambda t: torch.sigmoid(t) * t * 1.5}[act]
     act_id = {"gelu": Lb.ACT_GELU, "relu": Lb.ACT_RELU, "generic": -1}[act]
-    y, st = ops.moe_forward(x.cuda(), ids.cuda(), w1.cuda(), w2.cuda(), b1.cuda(), b2.cuda(), act_id, act_fn=fn)
-    dx, dw1, dw2, db1, db2 = ops.moe_backward(st, dy.cuda(), w1.cuda(), w2.cuda(), act_id, grad_dtype=torch.float32)
+    # 16-bit data must run on the tensor-core kernels whatever the hidden width (no silent CUDA-core fallback)
+    engine = Lb.ENGINE_TCGEN05 if dtype != torch.float32 else Lb.ENGINE_AUTO
+    y, st = ops.moe_forward(x.cuda(), ids.cuda(), w1.cuda(), w2.cuda(), b1.cuda(), b2.cuda(), act_id, act_fn=fn, engine=engine)
+    dx, dw1, dw2, db1, db2 = ops.moe_backward(st, dy.cuda(), w1.cuda(), w2.cuda(), act_id, grad_dtype=torch.float32,
+                                              engine=engine)
     want = O.moe_layer(x, ids, w1, w2, b1, b2, fn, dy)
     tol = REL[dtype]
     for name, got, exp in (("y", y, want["y"]), ("dx", dx, want["dx"]), ("dw1", dw1, want["dw1"]), ("dw2", dw2, want["dw2"]),
