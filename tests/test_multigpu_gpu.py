@@ -117,7 +117,7 @@ def _run(data_centric, proportion, dtype_name):
         assert msg == "ok", f"rank {rank}: {msg}"
 
 
-@pytest.mark.parametrize("proportion,dtype_name", [(None, "float32"), ([0.625, 0.375], "bfloat16")])
+@pytest.mark.parametrize("proportion,dtype_name", [(None, "float32"), ([0.625, 0.375], "bfloat16"), (None, "bfloat16")])
 def test_data_centric_two_gpus(proportion, dtype_name):
     _run(True, proportion, dtype_name)
 
