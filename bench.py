@@ -35,6 +35,7 @@ WORKLOADS = {  # name -> (d_model, hidden, experts, default tokens per GPU)
     "c5": (2048, 8192, 64, 131072),
     "c2": (768, 3072, 32, 16384),
     "small": (256, 1024, 8, 8192),
+    "c3": (1024, 4096, 64, 65536),      # operator sweep only (--ops): Zipf(1.2)-skewed routing, some experts empty
 }
 
 
@@ -45,7 +46,11 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default: the workload's)")
-    ap.add_argument("--workload", default="c5", choices=["c5", "c2", "small", "c4"],
+    ap.add_argument("--ops", action="store_true",
+                    help="operator sweep instead of the module step: routing, ESMM forward (fc1 + GELU, fc2), ESMM input "
+                         "gradient (x2), ESTMM (x2), ESS (x2), gather and combine timed separately on one GPU, each "
+                         "with its roofline fraction (workloads c2: E=8 and E=32, uniform routing; c3: Zipf-skewed)")
+    ap.add_argument("--workload", default="c5", choices=["c5", "c2", "small", "c4", "c3"],
                     help="c5: the headline layer; c2: d=768/H=3072/E=32, 16384 tokens (operator-sweep config, sized for ncu "
                          "captures); small: d=256/H=1024/E=8, 8192 tokens (smoke); c4: the Swin-MoE-B-like network "
                          "(secondary: images/s through the whole synthetic model, 128 images of 192x192 per GPU)")
@@ -209,6 +214,95 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_ops(args, dev):
+    """Operator sweep on one GPU: every operator of the layer timed alone (CUDA events on the launching stream, 3
+    warm-up + `--steps` timed launches back to back; operands of one launch exceed L2 except at the `small` size).
+    Tensor-bound operators are reported against the burst cuBLAS bf16 figure (kernels timed alone), HBM-bound ones
+    against the measured copy bandwidth."""
+    import torch
+    from hexa_moe_b200 import _lib as L, ops
+    d, H, E_default, T = WORKLOADS[args.workload]
+    T = args.tokens or T
+    k = TOP_K
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        pk = json.load(open(path))
+        tf_peak, hbm_peak, src = float(pk["bf16_tflops"]), float(pk["hbm_gbs"]), "measured (burst cuBLAS bf16, copy bandwidth)"
+    else:
+        tf_peak, hbm_peak, src = 1590.0, 6650.0, "fallback"
+    dt = torch.bfloat16
+    results = []
+    for E in ((8, 32) if args.workload == "c2" else (E_default,)):
+        g = torch.Generator().manual_seed(0)
+        if args.workload == "c3":       # Gumbel top-2 over Zipf(1.2) probabilities, the 4 least likely experts never chosen
+            p = torch.arange(1, E + 1, dtype=torch.float64) ** -1.2
+            p = p[torch.randperm(E, generator=g)]
+            p[torch.argsort(p)[:4]] = 0
+            logit = torch.log(p / p.sum()).float().expand(T, E) - torch.log(-torch.log(torch.rand(T, E, generator=g)))
+        else:
+            logit = torch.randn(T, E, generator=g)
+        ids = torch.topk(logit, k, dim=1).indices.to(torch.int32).to(dev)
+        x = torch.randn(T, d, generator=g).to(dt).to(dev)
+        dy = torch.randn(T, d, generator=g).to(dt).to(dev)
+        w1 = (torch.randn(E, H, d, generator=g) / d ** 0.5).to(dt).to(dev)
+        w2 = (torch.randn(E, H, d, generator=g) / H ** 0.5).to(dt).to(dev)
+        b1 = (torch.randn(E, H, generator=g) * 0.02).to(dev)
+        b2 = (torch.randn(E, d, generator=g) * 0.02).to(dev)
+        r = ops.route(ids, E)
+        xs, dys = ops.gather_rows(x, r), ops.gather_rows(dy, r)
+        y1 = ops.sorted_buffer(r.row_capacity, H, dt, dev)
+        h, dh = torch.empty_like(y1), torch.empty_like(y1)
+        ys, dxs = torch.empty_like(xs), torch.empty_like(xs)
+        dw = torch.empty(E, H, d, dtype=dt, device=dev)
+        y = torch.empty(T, d, dtype=dt, device=dev)
+        ops.esmm(xs, w1, L.B_NK, r, b1, L.EPI_ACT, L.ACT_GELU, aux=y1, out=h)
+        N = T * k
+        fl = 2.0 * N * d * H
+        es = 2
+        cases = [
+            ("route", lambda: ops.route(ids, E), 0.0, 12.0 * N),
+            ("gather x -> sorted rows", lambda: ops.gather_rows(x, r, out=xs), 0.0, 2.0 * N * d * es),
+            ("ESMM fc1 + bias + GELU (forward)", lambda: ops.esmm(xs, w1, L.B_NK, r, b1, L.EPI_ACT, L.ACT_GELU, aux=y1, out=h), fl, 0.0),
+            ("ESMM fc2 + bias (forward)", lambda: ops.esmm(h, w2, L.B_KN, r, b2, L.EPI_LINEAR, out=ys), fl, 0.0),
+            ("combine routes (sum over k)", lambda: ops.combine_rows(ys, r, out=y), 0.0, (k + 1.0) * T * d * es),
+            ("ESS db2", lambda: ops.ess(dys, r), 0.0, 1.0 * N * d * es),
+            ("ESTMM dW2", lambda: ops.estmm(h, dys, r, out=dw), fl, 0.0),
+            ("ESMM input gradient of fc2 x GELU'", lambda: ops.esmm(dys, w2, L.B_NK, r, None, L.EPI_DACT, L.ACT_GELU, aux=y1, out=dh), fl, 0.0),
+            ("ESS db1", lambda: ops.ess(dh, r), 0.0, 1.0 * N * H * es),
+            ("ESTMM dW1", lambda: ops.estmm(dh, xs, r, out=dw), fl, 0.0),
+            ("ESMM input gradient of fc1", lambda: ops.esmm(dh, w1, L.B_KN, r, None, L.EPI_LINEAR, out=dxs), fl, 0.0),
+        ]
+        counts = r.counts.cpu()
+        ops_out = {}
+        for name, fn, flops, nbytes in cases:
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(args.steps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / args.steps
+            if flops:
+                ach = flops / (ms * 1e-3) / 1e12
+                ops_out[name] = dict(ms=round(ms, 4), bound="tensor", achieved=round(ach, 1), unit="TFLOP/s", frac=round(ach / tf_peak, 3))
+            else:
+                ach = nbytes / (ms * 1e-3) / 1e9
+                ops_out[name] = dict(ms=round(ms, 4), bound="hbm", achieved=round(ach, 1), unit="GB/s", frac=round(ach / hbm_peak, 3))
+        results.append(dict(experts=E, rows_per_expert_min=int(counts.min()), rows_per_expert_max=int(counts.max()),
+                            empty_experts=int((counts == 0).sum()), ops=ops_out))
+    esmm_fwd = [v for res in results for n_, v in res["ops"].items() if n_.startswith("ESMM fc")]
+    value = 100.0 * sum(v["frac"] for v in esmm_fwd) / len(esmm_fwd)
+    line = dict(metric="esmm_forward_pct_of_bf16_tensor_peak", value=value, unit="%", n_gpus=1, steps=args.steps, warmup=3,
+                higher_is_better=True, vs_baseline=None, dtype="bf16", data="synthetic",
+                config=dict(workload=args.workload + "-operator-sweep", tokens=T, d_model=d, hidden=H, top_k=k,
+                            routing="zipf(1.2), 4 experts masked" if args.workload == "c3" else "uniform"),
+                peaks=dict(tflops=tf_peak, hbm_gbs=hbm_peak, source=src), sweep=results)
+    print(json.dumps(line), flush=True)
+
+
 def run_swin(args, dev, rank, world, timed_factory=None):
     """Secondary workload: forward + backward of the synthetic Swin-MoE-B-like network (swin_moe_harness.py), bf16,
     data-centric at N > 1.  One JSON line with images/s and the MoE-layer token rate."""
@@ -323,6 +417,12 @@ def main():
     if world > 1:
         dist.barrier()
 
+    if args.ops:
+        if world > 1:
+            raise SystemExit("--ops is a single-GPU sweep")
+        return run_ops(args, dev)
+    if args.workload == "c3":
+        raise SystemExit("workload c3 is an operator sweep: add --ops")
     if args.workload == "c4":
         return run_swin(args, dev, rank, world, timed_factory=None)
     d, H, E, T_default = WORKLOADS[args.workload]
