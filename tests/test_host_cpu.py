@@ -46,6 +46,17 @@ def test_argument_errors_come_back_as_status_codes():
     assert rc == -1 and b"null" in h.hexa_last_error_string()
     rc = h.hexa_esmm(None, 0, None, 0, 0, 0, None, 0, None, 0, None, 0, None, None, None, None, 4, 128, 8, 8, 2, 0, 0, 0, None)
     assert rc == -1
+    # the gate step: expert count beyond the kernel's limit, top_k beyond the expert count (checked before any CUDA call)
+    assert h.hexa_gate_max_experts() == 512 and h.hexa_gate_workspace_bytes() >= 4
+    rc = h.hexa_gate_topk(None, 0, 16, 513, 1, None, None, None, None, None, 0, None)
+    assert rc == -1 and b"experts" in h.hexa_last_error_string()
+    rc = h.hexa_gate_topk(None, 0, 16, 8, 9, None, None, None, None, None, 0, None)
+    assert rc == -1 and b"top_k" in h.hexa_last_error_string()
+    rc = h.hexa_gate_loss_grad(None, 0, 16, 0, None, None, None, 0, None)
+    assert rc == -1
+    # the scatter form of ESTMM: no destination list
+    rc = h.hexa_estmm_scatter(None, 0, None, 0, None, 4, 128, 64, 64, None, 2, 64, 64 * 32, 32, 2, 2, None)
+    assert rc == -1 and b"null" in h.hexa_last_error_string()
 
 
 def _toy(**kw):
