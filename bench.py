@@ -34,6 +34,8 @@ TOP_K, LAYERS = 2, 2
 WORKLOADS = {  # name -> (d_model, hidden, experts, default tokens per GPU)
     "c5": (2048, 8192, 64, 131072),
     "c2": (768, 3072, 32, 16384),
+    "c5s": (2048, 8192, 8, 16384),      # the headline layer's d / hidden with 8 experts and 16384 tokens: same k-loop lengths
+                                        # and tile shapes as c5 at ~3 GB resident (sized for ncu captures)
     "small": (256, 1024, 8, 8192),
     "c3": (1024, 4096, 64, 65536),      # operator sweep only (--ops): Zipf(1.2)-skewed routing, some experts empty
 }
@@ -50,7 +52,7 @@ def parse():
                     help="operator sweep instead of the module step: routing, ESMM forward (fc1 + GELU, fc2), ESMM input "
                          "gradient (x2), ESTMM (x2), ESS (x2), gather and combine timed separately on one GPU, each "
                          "with its roofline fraction (workloads c2: E=8 and E=32, uniform routing; c3: Zipf-skewed)")
-    ap.add_argument("--workload", default="c5", choices=["c5", "c2", "small", "c4", "c3"],
+    ap.add_argument("--workload", default="c5", choices=["c5", "c5s", "c2", "small", "c4", "c3"],
                     help="c5: the headline layer; c2: d=768/H=3072/E=32, 16384 tokens (operator-sweep config, sized for ncu "
                          "captures); small: d=256/H=1024/E=8, 8192 tokens (smoke); c4: the Swin-MoE-B-like network "
                          "(secondary: images/s through the whole synthetic model, 128 images of 192x192 per GPU)")

@@ -30,6 +30,9 @@ SIGNATURES = {
     "hexa_version": (ci, []),
     "hexa_last_error_string": (C.c_char_p, []),
     "hexa_set_status_word": (ci, [vp]),
+    "hexa_pending_device_status": (ci, []),
+    "hexa_set_wait_limit_ns": (ci, [C.c_uint64]),
+    "hexa_set_tc_debug": (ci, [ci]),
     "hexa_set_sm_limit": (ci, [ci]),
     "hexa_route_row_capacity": (i64, [i64, ci, ci, ci]),
     "hexa_route_workspace_bytes": (sz, [i64, ci, ci]),
@@ -80,9 +83,55 @@ def lib():
     return _lib
 
 
+ERR_DEVICE = -5
+_STATUS_CODES = {1: "the TMA producer waited for a free ring slot", 2: "the MMA issuer waited for a drained accumulator",
+                 3: "the MMA issuer waited for operands", 4: "an epilogue warp waited for an accumulator"}
+
+
 def check(status: int, what: str):
+    """Raise on a non-zero return code, and on a code that a kernel launched earlier left in the device's status
+    word (a bounded wait that ran out): the host sees it at its next call into the library, without synchronising."""
     if status != 0:
         raise HexaError(f"{what} failed ({status}): {lib().hexa_last_error_string().decode()}")
+    if _status_words:
+        code = lib().hexa_pending_device_status()
+        if code:
+            raise HexaError(f"{what}: a kernel on this device gave up a bounded wait (status code {code}: "
+                            f"{_STATUS_CODES.get(code, 'unknown')}); results since then are incomplete ({ERR_DEVICE})")
+
+
+# One status word per device in pinned host memory: kernels store a code there when a wait inside them runs out,
+# the host reads it without a copy.  Installed the first time an operator runs on a device.
+_status_words = {}
+
+
+def ensure_status_word(device_index: int):
+    w = _status_words.get(device_index)
+    if w is None:
+        with _lock:
+            w = _status_words.get(device_index)
+            if w is None:
+                w = torch.zeros(1, dtype=torch.int32).pin_memory()
+                with torch.cuda.device(device_index):
+                    rc = lib().hexa_set_status_word(w.data_ptr())
+                if rc != 0:
+                    raise HexaError(f"hexa_set_status_word failed ({rc}): {lib().hexa_last_error_string().decode()}")
+                _status_words[device_index] = w
+    return w
+
+
+def device_status(device_index: int = None) -> int:
+    """Code in the status word of a device (0: no kernel has reported a failure)."""
+    idx = torch.cuda.current_device() if device_index is None else device_index
+    w = _status_words.get(idx)
+    return 0 if w is None else int(w[0])
+
+
+def clear_device_status(device_index: int = None):
+    idx = torch.cuda.current_device() if device_index is None else device_index
+    w = _status_words.get(idx)
+    if w is not None:
+        w.zero_()
 
 
 def dt(t: torch.Tensor) -> int:
@@ -99,4 +148,7 @@ def ptr(t) -> int:
 def stream_of(t: torch.Tensor) -> int:
     if not t.is_cuda:
         raise HexaError("hexa_moe_b200 operators run on CUDA tensors only (no CPU path)")
+    idx = t.device.index
+    if idx not in _status_words:
+        ensure_status_word(torch.cuda.current_device() if idx is None else idx)
     return torch.cuda.current_stream(t.device).cuda_stream

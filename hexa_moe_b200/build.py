@@ -37,8 +37,7 @@ def build(force=False, verbose=False):
         return LIB
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
-    flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
-             "--use_fast_math" if False else "-DHEXA_NO_FAST_MATH"]
+    flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
     if verbose:
         flags += ["-Xptxas", "-v"]
     objs = []

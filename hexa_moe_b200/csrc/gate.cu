@@ -6,8 +6,14 @@
 // recomputes the softmax from the logits it has to read anyway.
 //
 // One warp per token, lane l holding columns l, l+32, ...; column sums stay in registers across the tokens of a
-// warp and meet in shared memory once per block, so the loop has no atomics except the top-1 histogram.
-// Ties: the lowest expert id wins, and the k ids of a token come out in descending score order.
+// warp, meet in shared memory once per block (one row per warp, added in warp order) and leave the block as one
+// partial row in the workspace; the block that finishes last adds the partial rows in block order.  Every float
+// sum therefore has a fixed order: mass and loss are bit-identical from run to run.  The only atomics are the
+// integer top-1 histogram and the completion ticket.
+// Ties: the lowest expert id wins, and the k ids of a token come out in descending score order.  The selection is
+// total: a score that is NaN ranks below every number, so a row of NaN / inf logits (an overflowed fp16 step) still
+// yields k distinct ids in [0, E) - the lowest free columns - and only the loss carries the NaN, as it does through
+// F.softmax -> torch.topk in the reference.
 #include <float.h>
 
 #include "hexa_common.cuh"
@@ -16,7 +22,10 @@ namespace hexa {
 namespace {
 
 constexpr int kGateThreads = 256;
+constexpr int kGateWarps = kGateThreads / 32;
 constexpr int kGateMaxExperts = 512;
+constexpr int kGateMaxBlocks = 1024;   // partial-mass rows the workspace holds
+constexpr size_t kGateTicketBytes = 256;
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -55,16 +64,16 @@ template <int VPT>
 __global__ void __launch_bounds__(kGateThreads)
 gate_topk_kernel(const float* __restrict__ logits, int64_t ld, int64_t T, int E, int k, int32_t* __restrict__ ids,
                  float* __restrict__ mass, int32_t* __restrict__ first_count, float* __restrict__ loss,
-                 unsigned int* __restrict__ ticket) {
-  __shared__ float mass_s[32 * VPT];
+                 unsigned int* __restrict__ ticket, float* __restrict__ partial) {
+  __shared__ float mass_w[kGateWarps][32 * VPT];
   __shared__ int cnt_s[32 * VPT];
-  __shared__ float red_s[kGateThreads / 32];
+  __shared__ float red_s[kGateWarps];
   __shared__ bool last_s;
-  for (int e = threadIdx.x; e < 32 * VPT; e += blockDim.x) { mass_s[e] = 0.f; cnt_s[e] = 0; }
+  for (int e = threadIdx.x; e < 32 * VPT; e += blockDim.x) cnt_s[e] = 0;
   __syncthreads();
-  const int lane = threadIdx.x & 31;
-  const int64_t warp0 = (int64_t)blockIdx.x * (kGateThreads / 32) + (threadIdx.x >> 5);
-  const int64_t nwarps = (int64_t)gridDim.x * (kGateThreads / 32);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t warp0 = (int64_t)blockIdx.x * kGateWarps + warp;
+  const int64_t nwarps = (int64_t)gridDim.x * kGateWarps;
   float acc[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) acc[i] = 0.f;
@@ -75,12 +84,17 @@ gate_topk_kernel(const float* __restrict__ logits, int64_t ld, int64_t T, int E,
     for (int i = 0; i < VPT; ++i) acc[i] += s[i];
     unsigned int taken = 0;
     for (int j = 0; j < k; ++j) {
-      float best = -1.f;
+      // candidates: this lane's free columns; NaN counts as -inf, and the first free column is taken even at -inf,
+      // so some lane always has a candidate while fewer than E columns are taken (k <= E is checked by the host)
+      float best = -INFINITY;
       int bi = 0x7fffffff;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int c = lane + 32 * i;
-        if (c < E && !((taken >> i) & 1u) && s[i] > best) { best = s[i]; bi = c; }   // ascending c: first maximum stays
+        if (c < E && !((taken >> i) & 1u)) {
+          const float v = s[i] == s[i] ? s[i] : -INFINITY;
+          if (bi == 0x7fffffff || v > best) { best = v; bi = c; }   // ascending c: the first maximum stays
+        }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
@@ -88,24 +102,25 @@ gate_topk_kernel(const float* __restrict__ logits, int64_t ld, int64_t T, int E,
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
         if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
       }
-      if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+      const bool valid = (unsigned)bi < (unsigned)E;     // always true; kept so that no index derived from data is trusted
+      if (valid && (bi & 31) == lane) taken |= 1u << (bi >> 5);
       if (lane == 0) {
-        ids[(int64_t)j * T + t] = bi;
-        if (j == 0) atomicAdd(&cnt_s[bi], 1);
+        ids[(int64_t)j * T + t] = valid ? bi : -1;         // -1 is a row the routing kernel skips
+        if (j == 0 && valid) atomicAdd(&cnt_s[bi], 1);
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int c = lane + 32 * i;
-    if (c < E) atomicAdd(&mass_s[c], acc[i]);
-  }
+  for (int i = 0; i < VPT; ++i) mass_w[warp][lane + 32 * i] = acc[i];
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    atomicAdd(&mass[e], mass_s[e]);
+    float m = 0.f;
+#pragma unroll
+    for (int w = 0; w < kGateWarps; ++w) m += mass_w[w][e];
+    partial[(int64_t)blockIdx.x * E + e] = m;
     if (cnt_s[e]) atomicAdd(&first_count[e], cnt_s[e]);
   }
-  // the block that finishes last folds the two [E] vectors into the loss
+  // the block that finishes last adds the partial rows (in block order) and folds the two [E] vectors into the loss
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) last_s = atomicAdd(ticket, 1u) == gridDim.x - 1;
@@ -113,13 +128,19 @@ gate_topk_kernel(const float* __restrict__ logits, int64_t ld, int64_t T, int E,
   if (!last_s) return;
   __threadfence();
   float part = 0.f;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) part += __ldcg(mass + e) * (float)__ldcg(first_count + e);
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float m = 0.f;
+    for (unsigned b = 0; b < gridDim.x; ++b) m += __ldcg(partial + (int64_t)b * E + e);
+    mass[e] = m;
+    part += m * (float)__ldcg(first_count + e);
+  }
+  // fixed-order block reduction: lanes by xor tree, warps in index order
   part = warp_sum(part);
-  if (lane == 0) red_s[threadIdx.x >> 5] = part;
+  if (lane == 0) red_s[warp] = part;
   __syncthreads();
   if (threadIdx.x == 0) {
     float tot = 0.f;
-    for (int w = 0; w < kGateThreads / 32; ++w) tot += red_s[w];
+    for (int w = 0; w < kGateWarps; ++w) tot += red_s[w];
     loss[0] = tot * ((float)E / (float)T) / (float)T;
   }
 }
@@ -157,7 +178,8 @@ gate_loss_grad_kernel(const float* __restrict__ logits, int64_t ld, int64_t T, i
 
 int gate_grid(int64_t T) {
   const int64_t want = ceil_div(T, kGateThreads / 32);
-  const int64_t cap = (int64_t)sm_count() * 4;
+  int64_t cap = (int64_t)sm_count() * 4;
+  if (cap > kGateMaxBlocks) cap = kGateMaxBlocks;
   return (int)(want < cap ? (want > 0 ? want : 1) : cap);
 }
 
@@ -168,7 +190,9 @@ using namespace hexa;
 
 extern "C" int hexa_gate_max_experts(void) { return kGateMaxExperts; }
 
-extern "C" size_t hexa_gate_workspace_bytes(void) { return 16; }
+extern "C" size_t hexa_gate_workspace_bytes(void) {
+  return kGateTicketBytes + (size_t)kGateMaxBlocks * kGateMaxExperts * sizeof(float);   // ticket + partial-mass rows (2 MiB)
+}
 
 extern "C" int hexa_gate_topk(const float* logits, int64_t ld, int64_t num_tokens, int num_experts, int top_k, int32_t* ids,
                               float* mass, int32_t* first_count, float* loss, void* workspace, size_t workspace_bytes,
@@ -180,15 +204,17 @@ extern "C" int hexa_gate_topk(const float* logits, int64_t ld, int64_t num_token
   HEXA_REQUIRE(mass && first_count && loss && workspace && workspace_bytes >= hexa_gate_workspace_bytes(),
                "hexa_gate_topk: null output or workspace smaller than hexa_gate_workspace_bytes()");
   HEXA_REQUIRE(num_tokens == 0 || (logits && ids && ld >= num_experts), "hexa_gate_topk: null logits/ids or ld < experts");
+  HEXA_REQUIRE(aligned16(workspace), "hexa_gate_topk: workspace must be 16-byte aligned");
   HEXA_CUDA(cudaMemsetAsync(mass, 0, sizeof(float) * num_experts, stream));
   HEXA_CUDA(cudaMemsetAsync(first_count, 0, sizeof(int32_t) * num_experts, stream));
   HEXA_CUDA(cudaMemsetAsync(loss, 0, sizeof(float), stream));
   HEXA_CUDA(cudaMemsetAsync(workspace, 0, 16, stream));
   if (num_tokens == 0) return HEXA_OK;
   unsigned int* ticket = static_cast<unsigned int*>(workspace);
+  float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kGateTicketBytes);
   const int grid = gate_grid(num_tokens);
 #define HEXA_GATE_FWD(V) \
-  gate_topk_kernel<V><<<grid, kGateThreads, 0, stream>>>(logits, ld, num_tokens, num_experts, top_k, ids, mass, first_count, loss, ticket)
+  gate_topk_kernel<V><<<grid, kGateThreads, 0, stream>>>(logits, ld, num_tokens, num_experts, top_k, ids, mass, first_count, loss, ticket, partial)
   const int vpt = (num_experts + 31) / 32;
   if (vpt <= 1) HEXA_GATE_FWD(1);
   else if (vpt <= 2) HEXA_GATE_FWD(2);

@@ -43,7 +43,6 @@ constexpr int UMMA_K = 16;
 constexpr int kEpiWarps = 16;
 constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr uint32_t kABytes = BLOCK_M * BLOCK_K * 2;  // 16 KB
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 enum Mode { ESMM_NK = 0, ESMM_KN = 1, ESTMM = 2 };
 
@@ -71,8 +70,11 @@ struct Params {
   int is_bf16;      // 16-bit flavour of the inputs (and of 16-bit outputs)
   int out_f32;      // ESTMM: fp32 output
   int beta;         // ESTMM: accumulate into out
-  int debug;        // measurement aid (HEXA_TC_DEBUG): bit 0 = producer skips the TMA loads, bit 1 = MMA thread skips the MMAs
+  int debug;        // measurement / test aid (HEXA_TC_DEBUG, hexa_set_tc_debug): bit 0 = the producer skips the TMA loads and
+                    // arrives in their place, bit 1 = the MMA thread skips the MMAs, bit 2 = the producer neither loads
+                    // nor arrives, so that every wait of the pipeline runs into its limit
   int32_t* status;
+  uint64_t wait_limit_ns;   // limit of every mbarrier wait (hexa_set_wait_limit_ns; default 2 s)
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -118,19 +120,30 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// The status word may live in device memory or in pinned host memory (where the host can poll it without a copy), so
+// it is written with plain stores: the first code to arrive stays, and which of two simultaneous codes wins is immaterial.
+__device__ __forceinline__ void report_status(int32_t* status, int code) {
+  if (status) {
+    volatile int32_t* s = status;
+    if (*s == 0) *s = code;
+    __threadfence_system();
+  }
+}
+
 // Bounded wait.  Returns false when this CTA is aborting (its own limit ran out or another role's did).
-__device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int code) {
+__device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int code,
+                                       uint64_t limit_ns) {
   uint32_t spins = 0;
   uint64_t t0 = 0;
   while (!mbar_try_wait_hint(bar, parity, 4000u)) {
-    if ((++spins & 0x3F) == 0) {
+    if ((++spins & 0xF) == 0) {
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
+        report_status(status, code);
         return false;
       }
     }
@@ -139,9 +152,10 @@ __device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile 
 }
 
 // Fast path of a bounded wait: one try_wait inline, the timed loop only when the barrier is not ready yet.
-__device__ __forceinline__ bool mbar_wait_fast(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int code) {
+__device__ __forceinline__ bool mbar_wait_fast(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status, int code,
+                                               uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait(bar, parity, abort_flag, status, code);
+  return mbar_wait(bar, parity, abort_flag, status, code, limit_ns);
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, uint64_t* bar, int c0, int c1) {
@@ -415,6 +429,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* acc_empty = bars + 2 * kStages + 2;   // [2] epilogues -> MMA    (used in the leader CTA)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* group_abort = abort_flag + 1;   // [kEpiWarps / 4]: one per group of four epilogue warps
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = CTAS == 2 ? (int)cluster_ctarank() : 0;    // 0 = leader of the pair
@@ -425,6 +440,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], kEpiWarps * CTAS); }
     *abort_flag = 0;
+    for (int g = 0; g < kEpiWarps / 4; ++g) group_abort[g] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // the allocating warp also frees; with CTAS = 2 the same warp of both CTAs takes part
@@ -451,11 +467,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t lead_full0 = CTAS == 2 ? map_to_cta(&full[0], 0) : 0u;   // the leader CTA's first full barrier
       for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step) {
         for (int kb = 0; kb < tile.num_kb; ++kb) {
-          if (!(ok = mbar_wait_fast(&empty[stage], phase ^ 1, abort_flag, p.status, 1))) break;
+          if (!(ok = mbar_wait_fast(&empty[stage], phase ^ 1, abort_flag, p.status, 1, p.wait_limit_ns))) break;
           uint8_t* sA = smem + (size_t)stage * C::kStageBytes;
           uint8_t* sB = sA + kABytes;
           const int bcol = tile.col0 + rank * BNH;     // this CTA's share of the B columns
-          if (p.debug & 1) {   // results are garbage; only the timing of the remaining pipeline is of interest
+          if (p.debug & 4) {
+            // nothing is loaded and nobody arrives: the consumers' waits run into their limit (error-path test)
+          } else if (p.debug & 1) {   // results are garbage; only the timing of the remaining pipeline is of interest
             if (rank == 0) mbar_arrive(&full[stage]);
           } else if (CTAS == 2) {
             // bytes of both CTAs are credited to the leader's barrier; only the leader arms it
@@ -528,12 +546,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-        if (!(ok = mbar_wait_fast(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, 2))) break;
+        if (!(ok = mbar_wait_fast(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, 2, p.wait_limit_ns))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         uint32_t accumulate = 0;
         for (int kb = 0; kb < tile.num_kb; ++kb) {
-          if (!(ok = mbar_wait_fast(&full[stage], phase, abort_flag, p.status, 3))) break;
+          if (!(ok = mbar_wait_fast(&full[stage], phase, abort_flag, p.status, 3, p.wait_limit_ns))) break;
           const uint64_t adesc = adesc0 + (uint64_t)stage * kStageDesc;
           const uint64_t bdesc = bdesc0 + (uint64_t)stage * kStageDesc;
           if (!(p.debug & 2)) {
@@ -572,7 +590,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-      if (!(ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4))) break;
+      // The four warps of a group meet at named barriers inside the tile, so they must leave together: each warp
+      // publishes a failed wait, the group synchronises, and all four read the same verdict.
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4, p.wait_limit_ns) && lane == 0) group_abort[part] = 1;
+      group_sync(1 + part);
+      if (group_abort[part]) { ok = false; break; }
       tc_fence_after();
       const int rloc = q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
@@ -807,7 +829,6 @@ int env_int(const char* name, int dflt) {
   return s ? atoi(s) : dflt;
 }
 // HEXA_TC_CTAS=1 keeps every GEMM on single-CTA tiles (for A/B measurements); default: CTA pairs where they apply.
-int debug_flags() { static int v = -1; if (v < 0) v = env_int("HEXA_TC_DEBUG", 0); return v; }
 bool pairs_enabled() { static int v = -1; if (v < 0) v = env_int("HEXA_TC_CTAS", 2) == 1 ? 0 : 1; return v == 1; }
 
 }  // namespace
@@ -876,7 +897,7 @@ int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int6
   p.pair_block = pair_block; p.max_pairs = row_cap / (2 * BLOCK_M) + E;
   p.bias = bias; p.ldbias = ldbias; p.aux = aux; p.ldaux = ldaux; p.c = c; p.ldc = ldc;
   p.n = n_out; p.k = k; p.m = 0; p.E = E; p.epilogue = epilogue; p.act = act; p.is_bf16 = is_bf16;
-  p.status = status_word(); p.debug = debug_flags();
+  p.status = status_word(); p.debug = tc_debug_flags(); p.wait_limit_ns = wait_limit_ns();
   const int64_t NT = ceil_div(n_out, BN);
   if (ctas == 2) {
     const int64_t max_tiles = p.max_pairs * NT;
@@ -931,7 +952,7 @@ int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, con
   p.n_split = n_split;
   for (int i = 0; i < n_split && i < 16; ++i) p.c_split[i] = split_out[i];
   p.is_bf16 = is_bf16; p.out_f32 = out_dtype == HEXA_F32; p.beta = beta;
-  p.status = status_word(); p.debug = debug_flags();
+  p.status = status_word(); p.debug = tc_debug_flags(); p.wait_limit_ns = wait_limit_ns();
   const int64_t max_tiles = (int64_t)E * ceil_div(m, BLOCK_M * ctas) * ceil_div(n, BN);
   // ESTMM stores straight from registers; the two output maps are unused placeholders
   if (ctas == 2) return launch<256, ESTMM, 2>(tmA, tmB, tmA, tmA, p, max_tiles, stream);

@@ -13,7 +13,22 @@ namespace hexa {
 
 // ---- host-side error plumbing -----------------------------------------------------------------
 void set_error(const char* fmt, ...);
-int32_t* status_word();  // per-thread device status word (may be null)
+int32_t* status_word();   // status word of the current device (may be null), see hexa_set_status_word
+int status_pending();     // code an earlier kernel left in the current device's status word, when the host can read it (else 0)
+uint64_t wait_limit_ns(); // limit of the bounded waits inside kernels, see hexa_set_wait_limit_ns
+int tc_debug_flags();     // HEXA_TC_DEBUG / hexa_set_tc_debug
+
+// Entry points that launch kernels with bounded waits refuse to run once such a wait has been given up on this
+// device: what those kernels wrote is incomplete, and so is everything computed from it.
+#define HEXA_CHECK_DEVICE_STATUS(name)                                                                     \
+  do {                                                                                                     \
+    const int code_ = ::hexa::status_pending();                                                            \
+    if (code_ != 0) {                                                                                      \
+      ::hexa::set_error("%s: an earlier kernel on this device gave up a bounded wait (status code %d); "   \
+                        "its outputs are incomplete.  Clear the status word to continue", name, code_);    \
+      return HEXA_ERR_DEVICE;                                                                              \
+    }                                                                                                      \
+  } while (0)
 
 #define HEXA_REQUIRE(cond, ...)          \
   do {                                   \

@@ -5,6 +5,47 @@
 
 using namespace hexa;
 
+namespace {
+// A kernel on device `dev` is about to store through `ptr`.  Memory of another GPU is reachable only after
+// cudaDeviceEnablePeerAccess from the storing device (access in the opposite direction, which is all that peer
+// copies into this GPU need, does not help), so it is enabled here, once per device pair, or the call is refused.
+int ensure_store_access(const void* ptr, int dev, const char* who) {
+  static unsigned char enabled[64][64];
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, ptr) != cudaSuccess) {
+    (void)cudaGetLastError();
+    set_error("%s: cannot classify destination pointer %p", who, ptr);
+    return HEXA_ERR_INVALID;
+  }
+  if (at.type != cudaMemoryTypeDevice && at.type != cudaMemoryTypeManaged) {
+    set_error("%s: destination %p is not device memory", who, ptr);
+    return HEXA_ERR_INVALID;
+  }
+  const int owner = at.device;
+  if (at.type == cudaMemoryTypeManaged || owner == dev) return HEXA_OK;
+  if (owner < 0 || owner >= 64) {
+    set_error("%s: destination %p belongs to device %d (out of range)", who, ptr, owner);
+    return HEXA_ERR_UNSUPPORTED;
+  }
+  if (__atomic_load_n(&enabled[dev][owner], __ATOMIC_ACQUIRE)) return HEXA_OK;
+  int can = 0;
+  if (cudaDeviceCanAccessPeer(&can, dev, owner) != cudaSuccess || !can) {
+    (void)cudaGetLastError();
+    set_error("%s: device %d cannot access the memory of device %d that destination %p lives in", who, dev, owner, ptr);
+    return HEXA_ERR_UNSUPPORTED;
+  }
+  const cudaError_t e = cudaDeviceEnablePeerAccess(owner, 0);
+  if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+    set_error("%s: cudaDeviceEnablePeerAccess(%d) from device %d failed: %s", who, owner, dev, cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return HEXA_ERR_UNSUPPORTED;
+  }
+  (void)cudaGetLastError();
+  __atomic_store_n(&enabled[dev][owner], (unsigned char)1, __ATOMIC_RELEASE);
+  return HEXA_OK;
+}
+}  // namespace
+
 extern "C" int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
                          const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
                          const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
@@ -22,6 +63,7 @@ extern "C" int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout
   HEXA_REQUIRE(act >= HEXA_ACT_NONE && act <= HEXA_ACT_SILU, "hexa_esmm: bad activation %d", act);
   HEXA_REQUIRE(epilogue != HEXA_EPI_DACT || aux, "hexa_esmm: HEXA_EPI_DACT needs the saved pre-activation in aux");
   HEXA_REQUIRE(engine >= HEXA_ENGINE_AUTO && engine <= HEXA_ENGINE_SIMT, "hexa_esmm: bad engine %d", engine);
+  HEXA_CHECK_DEVICE_STATUS("hexa_esmm");
   const bool tc_ok = esmm_tc_supported(a, lda, b, ldb, b_estride, aux, ldaux, c, ldc, bias, ldbias, n_out, dtype);
   if (engine == HEXA_ENGINE_TCGEN05 && !tc_ok) {
     set_error("hexa_esmm: tcgen05 engine needs 16-bit data, 16-byte aligned pointers and leading dimensions / n_out that are multiples of 8");
@@ -48,6 +90,7 @@ extern "C" int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq
   HEXA_REQUIRE(out_dtype == HEXA_F32 || out_dtype == dtype, "hexa_estmm: out_dtype must be fp32 or the input dtype");
   HEXA_REQUIRE(beta == 0 || beta == 1, "hexa_estmm: beta must be 0 or 1");
   HEXA_REQUIRE(engine >= HEXA_ENGINE_AUTO && engine <= HEXA_ENGINE_SIMT, "hexa_estmm: bad engine %d", engine);
+  HEXA_CHECK_DEVICE_STATUS("hexa_estmm");
   const bool tc_ok = estmm_tc_supported(p, ldp, q, ldq, out, ldo, o_estride, split_stride, n, dtype, out_dtype);
   if (engine == HEXA_ENGINE_TCGEN05 && !tc_ok) {
     set_error("hexa_estmm: tcgen05 engine needs 16-bit inputs, 16-byte aligned pointers and leading dimensions / n that are multiples of 8");
@@ -72,8 +115,14 @@ extern "C" int hexa_estmm_scatter(const void* p, int64_t ldp, const void* q, int
   HEXA_REQUIRE(ldp >= m && ldq >= n && ldo >= n && o_estride >= (m_split - 1) * ldo + n, "hexa_estmm_scatter: leading dimension too small");
   HEXA_REQUIRE(dtype == HEXA_F16 || dtype == HEXA_BF16, "hexa_estmm_scatter: 16-bit inputs only");
   HEXA_REQUIRE(out_dtype == HEXA_F32 || out_dtype == dtype, "hexa_estmm_scatter: out_dtype must be fp32 or the input dtype");
+  HEXA_CHECK_DEVICE_STATUS("hexa_estmm_scatter");
+  int dev = 0;
+  HEXA_CUDA(cudaGetDevice(&dev));
+  HEXA_REQUIRE(dev >= 0 && dev < 64, "hexa_estmm_scatter: device ordinal %d out of range", dev);
   for (int i = 0; i < n_split; ++i) {
     HEXA_REQUIRE(split_out[i], "hexa_estmm_scatter: split_out[%d] is null", i);
+    const int rc = ensure_store_access(split_out[i], dev, "hexa_estmm_scatter");
+    if (rc != HEXA_OK) return rc;
     if (!estmm_tc_supported(p, ldp, q, ldq, split_out[i], ldo, o_estride, 0, n, dtype, out_dtype)) {
       set_error("hexa_estmm_scatter: needs 16-byte aligned pointers and leading dimensions / n that are multiples of 8");
       return HEXA_ERR_UNSUPPORTED;

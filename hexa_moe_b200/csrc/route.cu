@@ -8,6 +8,7 @@
 //                    pad_offsets[e] + (rows of e in earlier chunks) + (rows of e earlier in the chunk)
 // HBM traffic: ids are read twice (8 B per routed row), row_token and token_row written once.
 #include <stdarg.h>
+#include <stdlib.h>
 
 #include "hexa_common.cuh"
 
@@ -181,7 +182,6 @@ __global__ void route_scatter(const int32_t* __restrict__ ids, int64_t T, int to
 
 // ---- error plumbing shared by every translation unit ------------------------------------------
 static thread_local char g_err[512] = "no error";
-static thread_local int32_t* g_status = nullptr;
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -189,7 +189,41 @@ void set_error(const char* fmt, ...) {
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
 }
-int32_t* status_word() { return g_status; }
+
+// Status words are per device, not per host thread: the kernels of one training step are launched from the
+// Python thread (forward) and from the autograd engine's thread (backward), and both must report to the same word.
+struct StatusSlot {
+  int32_t* word;        // where kernels store their code (device-accessible)
+  int host_readable;    // the word lives in pinned host memory: entry points can look at it before they launch
+};
+static StatusSlot g_status[64];
+static uint64_t g_wait_limit_ns = 2000000000ull;
+static int g_tc_debug = -1;
+
+static int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  return dev;
+}
+int32_t* status_word() {
+  const int dev = current_device();
+  return dev < 0 ? nullptr : __atomic_load_n(&g_status[dev].word, __ATOMIC_ACQUIRE);
+}
+int status_pending() {
+  const int dev = current_device();
+  if (dev < 0) return 0;
+  int32_t* w = __atomic_load_n(&g_status[dev].word, __ATOMIC_ACQUIRE);
+  if (!w || !g_status[dev].host_readable) return 0;
+  return (int)*reinterpret_cast<volatile int32_t*>(w);
+}
+uint64_t wait_limit_ns() { return g_wait_limit_ns; }
+int tc_debug_flags() {
+  if (g_tc_debug < 0) {
+    const char* s = getenv("HEXA_TC_DEBUG");
+    g_tc_debug = s ? atoi(s) : 0;
+  }
+  return g_tc_debug;
+}
 
 static int g_sm_limit = 0;
 int sm_limit() { return g_sm_limit; }
@@ -217,7 +251,27 @@ extern "C" int hexa_set_sm_limit(int n) {
 }
 extern "C" const char* hexa_last_error_string(void) { return hexa::g_err; }
 extern "C" int hexa_set_status_word(int32_t* status) {
-  hexa::g_status = status;
+  const int dev = hexa::current_device();
+  HEXA_REQUIRE(dev >= 0, "hexa_set_status_word: no current CUDA device (or ordinal >= 64)");
+  int host = 0;
+  if (status) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, status) == cudaSuccess) host = at.type == cudaMemoryTypeHost;
+    else (void)cudaGetLastError();
+  }
+  hexa::g_status[dev].host_readable = host;
+  __atomic_store_n(&hexa::g_status[dev].word, status, __ATOMIC_RELEASE);
+  return HEXA_OK;
+}
+extern "C" int hexa_pending_device_status(void) { return hexa::status_pending(); }
+extern "C" int hexa_set_wait_limit_ns(uint64_t ns) {
+  HEXA_REQUIRE(ns >= 1000, "hexa_set_wait_limit_ns: the limit must be at least 1000 ns");
+  hexa::g_wait_limit_ns = ns;
+  return HEXA_OK;
+}
+extern "C" int hexa_set_tc_debug(int flags) {
+  HEXA_REQUIRE(flags >= 0 && flags < 8, "hexa_set_tc_debug: flags must be a combination of bits 0..2");
+  hexa::g_tc_debug = flags;
   return HEXA_OK;
 }
 

@@ -333,18 +333,29 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
             kw = dict(ranks=W) if packed else {}
             kw2 = dict(kw, dw_out=cfg.cache.grad_buffer("fc2", stage)) if packed else {}
             dh, dw2, db2 = be.moe_backward_fc2(st, dy, w2, cfg.act_id, has_b2=ctx.has_b2, grad_dtype=w2_dt, **kw2)
-            if W > 1:   # reductions run on the side stream; the results are handed to the parameters when backward ends
-                cfg.cache.reduce_deferred(stage, "fc2", dw2, None if db2 is None else db2.to(b2_dt), split, rank, packed)
+            # By default the reduced gradients are added to the parameters' .grad by a callback at the end of the
+            # backward pass (nothing waits for the transfer); HEXA_DEFER_GRADS=0 returns them through autograd instead
+            # (hooks, torch.autograd.grad and wrappers that inspect the returned gradients then see them).
+            defer = os.environ.get("HEXA_DEFER_GRADS", "1") != "0"
+            red = {}
+            if W > 1:   # reductions run on the side stream
+                red["fc2"] = cfg.cache.reduce_deferred(stage, "fc2", dw2, None if db2 is None else db2.to(b2_dt), split, rank,
+                                                       packed, defer=defer)
                 cfg.cache.limit_compute_sms(cfg.cache.reduce_uses_sms())
             if packed:
                 kw["dw_out"] = cfg.cache.grad_buffer("fc1", stage)
             if W > 1:   # fc1's gradients start their reduction before the input-gradient GEMM is even launched
-                kw["after_dw"] = lambda g, b: cfg.cache.reduce_deferred(stage, "fc1", g, None if b is None else b.to(b1_dt),
-                                                                        split, rank, packed)
+                def _after(g, b):
+                    red["fc1"] = cfg.cache.reduce_deferred(stage, "fc1", g, None if b is None else b.to(b1_dt), split, rank,
+                                                           packed, defer=defer)
+                kw["after_dw"] = _after
             dx, dw1, db1 = be.moe_backward_fc1(st, dh, w1, has_b1=ctx.has_b1, grad_dtype=w1_dt, **kw)
             if W > 1:
                 cfg.cache.release(stage)
-                dw1 = dw2 = db1 = db2 = None
+                if defer:
+                    dw1 = dw2 = db1 = db2 = None
+                else:
+                    (dw2, db2), (dw1, db1) = red["fc2"], red["fc1"]
         else:
             sizes = ctx.sizes
             w1, w2 = ctx.local_w

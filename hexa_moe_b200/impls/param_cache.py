@@ -17,12 +17,89 @@ with events, so no host thread ever blocks.
 from __future__ import annotations
 
 import os
-from typing import List, Optional
+import threading
+import time
+from typing import Callable, List, Optional
 
 import torch
 import torch.distributed as dist
 
+from .._lib import HexaError
 from . import layers as _layers
+
+
+class BarrierWatchdog:
+    """Host-side deadline for stream waits that only another rank can release.
+
+    The SM-free barrier between ranks is a `cuStreamWaitValue32` on a word that a peer writes: if that peer has
+    raised, exited or taken another branch, the wait never ends, every stream ordered after it stalls, and the host
+    blocks for good at its next synchronisation.  Every barrier therefore registers here a `done()` probe (an event
+    recorded right behind the wait).  A daemon thread polls the oldest probes; one that stays unfinished for
+    `timeout_s` after it was enqueued trips the watchdog: `release()` is called once (it writes the awaited values
+    from a second stream, so the stalled streams drain - with meaningless data), `failed` names the barrier, and the
+    owner raises `HexaError` at its next call instead of hanging.  No kernel spins and nothing faults.
+    """
+
+    def __init__(self, timeout_s: float, release: Callable[[], None], poll_s: float = 0.05, clock=time.monotonic,
+                 on_thread_start: Optional[Callable[[], None]] = None):
+        self.timeout_s, self.release, self.poll_s, self.clock = float(timeout_s), release, poll_s, clock
+        self.on_thread_start = on_thread_start
+        self.failed: Optional[str] = None
+        self._items = []                 # (done, tag, enqueue time), oldest first
+        self._lock = threading.Lock()
+        self._thread: Optional[threading.Thread] = None
+        self._stop = threading.Event()
+
+    def watch(self, done: Callable[[], bool], tag: str):
+        with self._lock:
+            self._items.append((done, tag, self.clock()))
+            if self._thread is None and self.failed is None:
+                self._stop.clear()
+                self._thread = threading.Thread(target=self._run, name="hexa-barrier-watchdog", daemon=True)
+                self._thread.start()
+
+    def poll_once(self) -> bool:
+        """One pass of the watchdog (also what the thread runs).  Returns True when the deadline was hit."""
+        with self._lock:
+            while self._items and self._items[0][0]():
+                self._items.pop(0)
+            if not self._items or self.failed is not None:
+                return self.failed is not None
+            _done, tag, t0 = self._items[0]
+            if self.clock() - t0 <= self.timeout_s:
+                return False
+            self.failed = tag
+            self._items = []
+        try:
+            self.release()
+        except Exception as exc:  # noqa: BLE001  (the failure is reported either way)
+            self.failed = f"{tag} (and releasing the stalled streams failed: {exc})"
+        return True
+
+    def _run(self):
+        if self.on_thread_start is not None:
+            try:
+                self.on_thread_start()
+            except Exception:  # noqa: BLE001
+                pass
+        while not self._stop.wait(self.poll_s):
+            if self.poll_once():
+                return
+            with self._lock:
+                if not self._items:          # nothing outstanding: let the thread end, the next watch() restarts it
+                    self._thread = None
+                    return
+
+    def pending(self) -> int:
+        with self._lock:
+            return len(self._items)
+
+    def stop(self):
+        self._stop.set()
+        t = self._thread
+        if t is not None and t is not threading.current_thread():
+            t.join(timeout=2.0)
+        self._thread = None
 
 
 class PipelineSharedCache:
@@ -36,6 +113,45 @@ class PipelineSharedCache:
         self._pending = []
         self._callback_queued = False
         self._red = None          # peer-copy reduce-scatter state (buffers, flags), built on first use
+        self._watchdog: Optional[BarrierWatchdog] = None
+        self.timeline = None      # a list while a caller wants spans recorded: (site, stream name, start event, end event)
+
+    # -- instrumentation and health --------------------------------------------------------------
+    def _span(self, site: str, stream_name: str, stream):
+        """Context manager recording a pair of timing events around what the body enqueues on `stream`."""
+        cache = self
+
+        class _S:
+            def __enter__(self_):
+                self_.a = None
+                if cache.timeline is not None:
+                    self_.a = torch.cuda.Event(enable_timing=True)
+                    self_.a.record(stream)
+                return self_
+
+            def __exit__(self_, *exc):
+                if self_.a is not None and cache.timeline is not None:
+                    b = torch.cuda.Event(enable_timing=True)
+                    b.record(stream)
+                    cache.timeline.append((site, stream_name, self_.a, b))
+                return False
+        return _S()
+
+    def _compute_wait(self, ev, site: str):
+        """Order the current (compute) stream after `ev`; with a timeline, record how long that held it."""
+        if ev is None:
+            return
+        cur = torch.cuda.current_stream()
+        with self._span(site, "compute", cur):
+            cur.wait_event(ev)
+
+    def check_health(self):
+        """Raise if a barrier between ranks ran into its host-side deadline (a peer is gone or out of step)."""
+        wd = self._watchdog
+        if wd is not None and wd.failed is not None:
+            raise HexaError(f"pipeline-shared cache: {wd.failed} was not reached by every rank within "
+                            f"{wd.timeout_s:.0f} s (HEXA_BARRIER_TIMEOUT_S); the stalled streams were released, their "
+                            "data is meaningless; a peer has failed or left")
 
     # -- storage ---------------------------------------------------------------------------------
     def _ensure(self, device, dtype):
@@ -59,6 +175,16 @@ class PipelineSharedCache:
         if self.slots is not None:
             for s in self.slots:
                 s["stage"] = -1
+        # reductions queued by a backward pass that never finished (it raised) belong to no step any more
+        if self._callback_queued and not self._in_backward():
+            self._pending, self._callback_queued = [], False
+
+    @staticmethod
+    def _in_backward() -> bool:
+        try:
+            return bool(torch._C._current_graph_task_id() != -1)
+        except Exception:  # noqa: BLE001
+            return False
 
     # -- gather ----------------------------------------------------------------------------------
     def _views(self, slot, stage):
@@ -126,23 +252,24 @@ class PipelineSharedCache:
         views = self._views(slot, stage)
         if stage == 0 or self._sync_needed:
             # every rank's parameters are final (its optimizer has run) before anyone reads them
-            if self._red not in (None, False):
-                self._peer_barrier()
-            else:
-                dist.all_reduce(self._flag, group=o.group)
+            with self._span("gather.params_final_barrier", "side", self.side):
+                if self._red not in (None, False):
+                    self._peer_barrier("parameters-final barrier before the gather of layer %d" % stage)
+                else:
+                    dist.all_reduce(self._flag, group=o.group)
             self._sync_needed = False
         for kind in order:
             full = views[kind]
             if full is None:
                 continue
             inner = full.shape[2] if full.dim() == 3 else 1
-            off = 0
-            for r in range(W):
-                rr = (o.local_rank + 1 + r) % W                 # start with the neighbour: spreads the load over the links
-                src = self._peers[rr][stage][kind]
-                nloc = split[rr]
-                lo = sum(split[:rr])
-                _ops.copy_2d(full[:, lo: lo + nloc], full.stride(0), src, src.stride(0), nloc * inner, E)
+            with self._span("gather.copy_" + kind, "side", self.side):
+                for r in range(W):
+                    rr = (o.local_rank + 1 + r) % W             # start with the neighbour: spreads the load over the links
+                    src = self._peers[rr][stage][kind]
+                    nloc = split[rr]
+                    lo = sum(split[:rr])
+                    _ops.copy_2d(full[:, lo: lo + nloc], full.stride(0), src, src.stride(0), nloc * inner, E)
             ev = torch.cuda.Event()
             ev.record(self.side)
             slot["ready"][kind] = ev
@@ -183,6 +310,7 @@ class PipelineSharedCache:
         o = self.o
         if stage < 0 or stage >= o.total_depth_moe or o.world_size == 1:
             return
+        self.check_health()
         p = o.batched_fc1_w[stage]
         self._ensure(p.device, p.dtype)
         slot = self.slots[stage % 2]
@@ -215,9 +343,7 @@ class PipelineSharedCache:
     def wait(self, stage: int, kind: str):
         """Order the current stream after the arrival of one tensor ("w1", "w2" or "b1") of layer `stage`."""
         slot = self.slots[stage % 2]
-        ev = slot["ready"].get(kind)
-        if ev is not None:
-            torch.cuda.current_stream().wait_event(ev)
+        self._compute_wait(slot["ready"].get(kind), "wait." + kind)
 
     def get(self, stage: int, order=("w1", "b1", "w2"), wait=("w1", "b1", "w2")):
         """Full (w1 [E,H,d_in], w2 [E,H,d_out], b1 [E,H] | None) of layer `stage`.  Starts the gather if needed and
@@ -280,11 +406,13 @@ class PipelineSharedCache:
         self._red = red if int(flag.item()) == 1 else False
         return self._red is not False
 
-    def _peer_barrier(self):
+    def _peer_barrier(self, what: str = "barrier between ranks"):
         """Every rank's side stream has reached this point before any rank's side stream continues.  Each rank copies
         the next sequence number into its slot of every peer's flag array (4-byte peer copies) and then makes its
-        stream wait until all of its own slots have reached that number."""
+        stream wait until all of its own slots have reached that number.  The wait has no limit on the device; the
+        host-side watchdog gives it one (see BarrierWatchdog)."""
         from .. import ops as _ops
+        self.check_health()
         red, o = self._red, self.o
         red["seq"] += 1
         seq = red["seq"]
@@ -300,6 +428,32 @@ class PipelineSharedCache:
         for r in range(o.world_size):
             if r != o.local_rank:
                 _ops.stream_wait_value(red["flags"][r: r + 1], seq, stream)
+        ev = torch.cuda.Event()
+        ev.record(self.side)
+        self._watch_barrier(ev, "%s (sequence %d)" % (what, seq))
+
+    def _watch_barrier(self, ev, tag: str):
+        if self._watchdog is None:
+            timeout = float(os.environ.get("HEXA_BARRIER_TIMEOUT_S", "300"))
+            dev = self.side.device
+            self._watchdog = BarrierWatchdog(timeout, self._release_barriers,
+                                             on_thread_start=lambda: torch.cuda.set_device(dev))
+        self._watchdog.watch(ev.query, tag)
+
+    def _release_barriers(self):
+        """Watchdog action: write the newest awaited sequence number into this rank's own flag words from a second
+        stream, so that every stream wait enqueued so far completes and the stalled streams drain."""
+        from .. import ops as _ops
+        red, o = self._red, self.o
+        if red in (None, False):
+            return
+        seq = red["seq"]
+        val = red["seq_table"][seq - red["seq_base"] - 1: seq - red["seq_base"]]
+        with torch.cuda.device(self.side.device):
+            rescue = torch.cuda.Stream(device=self.side.device)
+            for r in range(o.world_size):
+                if r != o.local_rank:
+                    _ops.copy_2d(red["flags"][r: r + 1], 1, val, 1, 1, 1, stream=rescue.cuda_stream)
 
     def grad_buffer(self, which: str, stage: int):
         """Where ESTMM should write this layer's weight gradient so that the peer-copy reduce-scatter can read it:
@@ -310,9 +464,7 @@ class PipelineSharedCache:
         o = self.o
         W, E, loc = o.world_size, o.num_global_experts, o.local_dim_list[stage]
         d = o.input_dim_list_moe[stage] if which == "fc1" else o.output_dim_list_moe[stage]
-        ev = self._red["free"][(which, stage % 2)]
-        if ev is not None:
-            torch.cuda.current_stream().wait_event(ev)
+        self._compute_wait(self._red["free"][(which, stage % 2)], "wait.grad_buffer_free")
         return self._red["grad"][which][stage % 2][: W * E * loc * d].view(W, E, loc, d)
 
     def _reduce_peer(self, which: str, stage: int, out):
@@ -322,32 +474,40 @@ class PipelineSharedCache:
         W, rank = o.world_size, o.local_rank
         n = out.numel()
         par = stage % 2
-        self._peer_barrier()                                      # every rank's gradient is complete
+        with self._span("reduce.grads_complete_barrier", "side", self.side):
+            self._peer_barrier("gradients-complete barrier of %s, layer %d" % (which, stage))
         if red["recv"] is None:      # allocated on the side stream, the only stream that uses it
             red["recv"] = torch.empty(red["recv_elems"], device=out.device, dtype=out.dtype)
         recv = red["recv"][: (W - 1) * n].view(W - 1, n)
         i = 0
-        for k in range(1, W):
-            r = (rank + k) % W
-            src = red["peer_grad"][r][which][par][rank * n: (rank + 1) * n]
-            _ops.copy_2d(recv[i], n, src, n, n, 1, stream=self.side.cuda_stream)
-            i += 1
+        with self._span("reduce.copy", "side", self.side):
+            for k in range(1, W):
+                r = (rank + k) % W
+                src = red["peer_grad"][r][which][par][rank * n: (rank + 1) * n]
+                _ops.copy_2d(recv[i], n, src, n, n, 1, stream=self.side.cuda_stream)
+                i += 1
         local = red["grad"][which][par][rank * n: (rank + 1) * n]
-        _ops.mean_slices(local, recv, W - 1, W, out.view(-1))
-        self._peer_barrier()                                      # every rank has finished reading everyone's buffer
+        with self._span("reduce.mean_kernel", "side", self.side):
+            _ops.mean_slices(local, recv, W - 1, W, out.view(-1))
+        with self._span("reduce.readers_done_barrier", "side", self.side):
+            self._peer_barrier("readers-done barrier of %s, layer %d" % (which, stage))
         ev = torch.cuda.Event()
         ev.record(self.side)
         red["free"][(which, par)] = ev
 
     # -- gradient reduction ----------------------------------------------------------------------
-    def reduce_deferred(self, stage: int, which: str, dw, db, split: List[int], rank: int, packed: bool = False):
+    def reduce_deferred(self, stage: int, which: str, dw, db, split: List[int], rank: int, packed: bool = False,
+                        defer: bool = True):
         """Average one layer's expert gradients over the ranks without stalling the compute stream.
 
         dw [E, H, d*] (and db: [E, H] for "fc1", [E, d_out] for "fc2") are reduce-scattered along the hidden
-        dimension (fc2's bias: all-reduced) on the side stream.  The reduced slices are not returned through
-        autograd: they are accumulated into the parameters' .grad by a callback that the autograd engine runs
-        when the whole backward pass has finished, so the transfer overlaps everything that is still to run."""
+        dimension (fc2's bias: all-reduced) on the side stream.  With `defer` (the default) the reduced slices are
+        not returned through autograd: they are accumulated into the parameters' .grad by a callback that the
+        autograd engine runs when the whole backward pass has finished, so the transfer overlaps everything that is
+        still to run.  With defer=False the current stream waits for the reduction and the reduced (dw, db) are
+        returned, shaped like this rank's parameter slices, for the caller to hand to autograd."""
         o = self.o
+        self.check_health()
         if which == "fc1":
             targets = [(o.batched_fc1_w[stage], dw, True), (o.batched_fc1_bias[stage] if o.has_fc1_bias else None, db, True)]
         else:
@@ -374,7 +534,7 @@ class PipelineSharedCache:
             return outs
 
         if self.side is None:
-            self._pending.append((None, run(), None))
+            ev, outs, keep = None, run(), None
         else:
             cur = torch.cuda.current_stream()
             self.side.wait_stream(cur)
@@ -384,28 +544,43 @@ class PipelineSharedCache:
                 ev.record(self.side)
             # the inputs stay referenced until the flush (after the compute stream has waited for `ev`), so their
             # memory cannot be handed out again while the side stream still reads it
-            self._pending.append((ev, outs, [g for _, g, _ in targets]))
+            keep = [g for _, g, _ in targets]
+        if not defer:
+            self._compute_wait(ev, "wait.reduction_inline")
+            for _, g in outs:
+                if g.is_cuda:
+                    g.record_stream(torch.cuda.current_stream())
+            loc = split[rank]
+            red = {id(prm): (g[:, :loc] if sharded else g) for (prm, g), (_, _, sharded) in zip(outs, targets)}
+            w_prm = o.batched_fc1_w[stage] if which == "fc1" else o.batched_fc2_w[stage]
+            b_prm = (o.batched_fc1_bias[stage] if o.has_fc1_bias else None) if which == "fc1" else \
+                    (o.batched_fc2_bias[stage] if o.has_fc2_bias else None)
+            return red.get(id(w_prm)), (red.get(id(b_prm)) if b_prm is not None else None)
+        self._pending.append((ev, outs, keep))
         if not self._callback_queued:
             self._callback_queued = True
             torch.autograd.Variable._execution_engine.queue_callback(self._flush_grads)
+        return None, None
 
     def _flush_grads(self):
         """End of a backward pass: wait for the reductions and add their results to the parameters' .grad."""
-        self._callback_queued = False
         pending, self._pending = self._pending, []
-        for ev, outs, _keep in pending:
-            if ev is not None:
-                torch.cuda.current_stream().wait_event(ev)
-            for prm, g in outs:
-                if g.shape != prm.shape:        # a slice narrower than the stored (padded) parameter
-                    full = torch.zeros_like(prm)
-                    full[:, : g.shape[1]].copy_(g)
-                    g = full
-                if prm.grad is None:
-                    prm.grad = g
-                else:
-                    prm.grad.add_(g)
-        self.limit_compute_sms(False)
+        self._callback_queued = False
+        try:
+            self.check_health()
+            for ev, outs, _keep in pending:
+                self._compute_wait(ev, "wait.reductions_at_end_of_backward")
+                for prm, g in outs:
+                    if g.shape != prm.shape:        # a slice narrower than the stored (padded) parameter
+                        full = torch.zeros_like(prm)
+                        full[:, : g.shape[1]].copy_(g)
+                        g = full
+                    if prm.grad is None:
+                        prm.grad = g
+                    else:
+                        prm.grad.add_(g)
+        finally:
+            self.limit_compute_sms(False)
 
     def uses_sms(self) -> bool:
         """True when gathers run as NCCL kernels (the peer-copy path leaves every SM to the GEMMs)."""
@@ -417,9 +592,21 @@ class PipelineSharedCache:
 
     def close(self):
         """Drop the mappings of other ranks' memory (call on every rank before the process group is destroyed)."""
-        if self.side is not None:
+        wd, self._watchdog = self._watchdog, None
+        failed = wd is not None and wd.failed is not None
+        if wd is not None:
+            if not failed and self.side is not None and wd.pending():
+                # outstanding barriers get the same deadline here as anywhere else: never block on them for good
+                t0 = time.monotonic()
+                while wd.pending() and wd.failed is None and time.monotonic() - t0 < wd.timeout_s + 1.0:
+                    wd.poll_once()
+                    time.sleep(0.01)
+                failed = wd.failed is not None
+            wd.stop()
+        if self.side is not None and not failed:
             torch.cuda.synchronize()
         self._pending = []
+        self._callback_queued = False
         self._peers = None
         self._peer_ptrs = None
         self._red = None

@@ -76,10 +76,27 @@ int hexa_version(void);
 const char* hexa_last_error_string(void);
 
 /* Device status word for kernels with bounded waits (mbarrier spins in the tcgen05 kernels).
- * `status` points to one int32 in device memory that the caller zeroes once; a kernel that gives
- * up a wait stores a non-zero code there and returns.  Pass it with hexa_set_status_word (per
- * host thread); NULL disables reporting (waits stay bounded). */
+ * `status` points to one zeroed int32 that kernels on the CURRENT device can write: device memory, or pinned host
+ * memory (cudaHostAlloc / cudaHostRegister), which the host can read at any time without a copy or a synchronisation.
+ * A kernel that gives up a wait stores a non-zero code there (1 = producer waiting for a free ring slot, 2 = MMA
+ * issuer waiting for a drained accumulator, 3 = MMA issuer waiting for operands, 4 = epilogue waiting for an
+ * accumulator), lets copies in flight land, frees its tensor memory and returns; its outputs are incomplete.
+ * One word per device, shared by all host threads (forward and backward of a training step are launched from
+ * different threads).  With a word in pinned host memory, hexa_esmm / hexa_estmm / hexa_estmm_scatter return
+ * HEXA_ERR_DEVICE without launching while the word is non-zero; the caller zeroes the word to continue.
+ * NULL disables reporting (waits stay bounded).  Replaces, as the way a device-side failure reaches the host,
+ * HandleError's printf + exit(1) (hexa_moe_cuda/hexa_moe/kernels/esmm_half.cu:27-36). */
 int hexa_set_status_word(int32_t* status);
+/* Code currently in the current device's status word when that word is host-readable, else 0.  Never synchronises. */
+int hexa_pending_device_status(void);
+/* Limit of every wait inside the kernels, in nanoseconds of the GPU's global timer (process-wide; default 2 s). */
+int hexa_set_wait_limit_ns(uint64_t ns);
+/* Measurement / test switches of the tcgen05 kernels (process-wide; initial value: environment variable
+ * HEXA_TC_DEBUG, default 0).  bit 0: the TMA producer skips its loads and signals their arrival itself; bit 1: the
+ * MMA thread skips the MMAs (both: timing of the remaining pipeline, results are garbage); bit 2: the producer
+ * neither loads nor signals, so every wait of the pipeline runs into its limit and the kernel reports through the
+ * status word (used with a short hexa_set_wait_limit_ns to exercise the error path without any fault). */
+int hexa_set_tc_debug(int flags);
 
 /* Cap on the SMs the persistent GEMM kernels occupy from now on (process-wide; 0 = all SMs).  Their tile
  * schedule is static, so they should not share SMs with long-running kernels of other streams (collectives):
@@ -163,10 +180,12 @@ int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq, const int
  * gradient through torch.distributed, impls/layers.py:431-474): output row i of expert e is written at
  *   split_out[i / m_split] + e*o_estride + (i % m_split)*ldo            (elements of out_dtype)
  * split_out is a HOST array of n_split = ceil(m / m_split) <= 16 device pointers (copied at the call).  Meant for
- * laying a weight gradient out per owner of a hidden slice without a packing pass.  Verified for destinations in
- * the calling GPU's own memory only: with destinations in another GPU's memory (the reduce-scatter transfer done
- * by the GEMM's own stores) the CTA-pair kernel raised an illegal-address fault at 2 GiB buffers on two GPUs, the
- * cause is not known, and the library's multi-GPU path therefore does not use this entry point.
+ * laying a weight gradient out per owner of a hidden slice without a packing pass.  A destination may be another
+ * GPU's memory (the transfer of a reduce-scatter done by the GEMM's own stores): stores from the calling device need
+ * peer access in that direction, which peer copies INTO the calling device do not establish, so the entry point
+ * enables it itself (cudaDeviceEnablePeerAccess, once per device pair) and returns HEXA_ERR_UNSUPPORTED when the
+ * devices cannot reach each other, HEXA_ERR_INVALID for a destination that is not device memory.  (An earlier
+ * version left this to the caller and faulted with an illegal address on remote destinations.)
  * 16-bit inputs only (the tcgen05 kernel); the destination is overwritten (beta = 0). */
 int hexa_estmm_scatter(const void* p, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets,
                        int num_experts, int64_t row_capacity, int64_t m, int64_t n, void* const* split_out, int n_split,
@@ -226,7 +245,10 @@ int hexa_mean_slices(const void* local, const void* recv, int n_recv, int64_t el
  *   mass         float [num_experts]: column sums of softmax(logits)
  *   first_count  int32 [num_experts]: tokens whose first choice is the expert
  *   loss         float [1]: (E/T^2) * sum_e mass_e * first_count_e
- * All four are overwritten.  workspace: hexa_gate_workspace_bytes() bytes of device memory, contents irrelevant. */
+ * All four are overwritten.  Every floating-point sum has a fixed order (per-warp, per-block and per-grid partials added
+ * by index), so mass and loss are bit-identical from run to run.  A NaN score ranks below every number: a row of
+ * NaN / inf logits still yields top_k distinct ids in [0, num_experts) (the lowest free ones) and NaN in mass / loss.
+ * workspace: hexa_gate_workspace_bytes() bytes of 16-byte aligned device memory, contents irrelevant. */
 int hexa_gate_max_experts(void);
 size_t hexa_gate_workspace_bytes(void);
 int hexa_gate_topk(const float* logits, int64_t ld, int64_t num_tokens, int num_experts, int top_k, int32_t* ids,

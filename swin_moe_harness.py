@@ -5,12 +5,16 @@ Shape of the reference's Swin-MoE-B example (Swin-Transformer-MoE/configs/swinmo
 swin_moe_base_patch4_window12_192_*.yaml and models/swin_transformer_moe_cascaded.py:650-879): 4x4 patch embedding,
 stage dims 128/256/512/1024 with depths 2/2/18/2 and heads 4/8/16/32, window 12, patch merging between stages,
 every block's FFN served by ONE shared MoE_Cascaded (dense FFN in even blocks, MoE in every other block of stages 3
-and 4: 32 experts, top-1, mlp_ratio 4, no fc1 bias).  What is simplified, because this is a timing harness built
-from stock PyTorch ops and not a model to train: window attention is scaled-dot-product attention over (optionally
-rolled) windows without the shifted-window mask and without the continuous relative position bias.
+and 4: 32 experts, top-1, mlp_ratio 4, no fc1 bias).  Window attention follows the reference's blocks
+(models/swin_transformer_moe_cascaded.py:135-236, 256-407): scaled dot products plus a continuous relative position
+bias (a two-layer MLP over log-spaced relative coordinates, one value per head) and, in the shifted blocks, the
+mask that keeps tokens from different image regions of a rolled window apart.  It is built from stock PyTorch ops
+(one scaled_dot_product_attention call per block with an additive mask); drop-path, dropout and the window-process
+kernels of the reference are left out: this is a timing and parity harness, not a model to train.
 """
 from __future__ import annotations
 
+import math
 from typing import List
 
 import torch
@@ -20,25 +24,80 @@ import torch.nn.functional as F
 from hexa_moe import moe as hmoe
 
 
+def shifted_window_mask(hw: int, w: int, shift: int) -> torch.Tensor:
+    """Additive mask [windows, w*w, w*w] for windows cut from an hw x hw map rolled by `shift`: 0 between tokens that
+    come from the same region of the unrolled image, -100 otherwise (the value the reference adds, ...:338-354)."""
+    region = torch.zeros(hw, hw)
+    edges = (0, hw - w, hw - shift, hw)
+    for i in range(3):
+        for j in range(3):
+            region[edges[i]: edges[i + 1], edges[j]: edges[j + 1]] = 3 * i + j
+    nw = hw // w
+    per_window = region.view(nw, w, nw, w).permute(0, 2, 1, 3).reshape(nw * nw, w * w)
+    return (per_window.unsqueeze(1) != per_window.unsqueeze(2)).float() * -100.0
+
+
 class WindowAttention(nn.Module):
     def __init__(self, dim: int, heads: int, window: int, shift: int):
         super().__init__()
         self.heads, self.window, self.shift = heads, window, shift
         self.qkv = nn.Linear(dim, 3 * dim)
         self.proj = nn.Linear(dim, dim)
+        # continuous relative position bias: MLP(2 -> 512 -> heads) over the (2w-1)^2 possible offsets
+        self.cpb_mlp = nn.Sequential(nn.Linear(2, 512), nn.ReLU(inplace=True), nn.Linear(512, heads, bias=False))
+        self._tables = {}      # window size actually used -> (offset coordinates, offset index of every token pair)
+        self._masks = {}       # (hw, w) -> additive shift mask
+
+    def _bias_tables(self, w: int, device):
+        key = (w, device)
+        if key not in self._tables:
+            off = torch.arange(-(w - 1), w, dtype=torch.float32)
+            grid = torch.stack(torch.meshgrid(off, off, indexing="ij"), dim=-1) / max(w - 1, 1) * 8.0     # [2w-1, 2w-1, 2]
+            coords = torch.sign(grid) * torch.log2(grid.abs() + 1.0) / math.log2(8.0)
+            pos = torch.stack(torch.meshgrid(torch.arange(w), torch.arange(w), indexing="ij"), dim=0).flatten(1)   # [2, w*w]
+            rel = pos[:, :, None] - pos[:, None, :] + (w - 1)                                              # [2, N, N]
+            index = rel[0] * (2 * w - 1) + rel[1]
+            self._tables[key] = (coords.view(-1, 2).to(device), index.to(device))
+        return self._tables[key]
+
+    def additive_mask(self, hw: int, w: int, dtype, device) -> torch.Tensor:
+        """[1, windows * heads, N, N] (windows = 1 without a shift): relative position bias + shift mask."""
+        coords, index = self._bias_tables(w, device)
+        table = self.cpb_mlp(coords.to(self.cpb_mlp[0].weight.dtype))                  # [(2w-1)^2, heads]
+        bias = table[index.view(-1)].view(w * w, w * w, self.heads).permute(2, 0, 1)   # [heads, N, N]
+        if self.shift and w < hw:
+            key = (hw, w, device)
+            if key not in self._masks:
+                self._masks[key] = shifted_window_mask(hw, w, self.shift).to(device)
+            m = self._masks[key].to(bias.dtype)                                         # [windows, N, N]
+            bias = bias.unsqueeze(0) + m.unsqueeze(1)                                   # [windows, heads, N, N]
+            bias = bias.reshape(1, -1, w * w, w * w)
+        else:
+            bias = bias.unsqueeze(0)
+        return bias.to(dtype)
 
     def forward(self, x: torch.Tensor, hw: int) -> torch.Tensor:
         B, N, C = x.shape
         w = min(self.window, hw)
+        shifted = bool(self.shift) and w < hw
         x = x.view(B, hw, hw, C)
-        if self.shift and w < hw:
+        if shifted:
             x = torch.roll(x, shifts=(-self.shift, -self.shift), dims=(1, 2))
         nw = hw // w
-        x = x.view(B, nw, w, nw, w, C).permute(0, 1, 3, 2, 4, 5).reshape(B * nw * nw, w * w, C)
-        q, k, v = self.qkv(x).view(-1, w * w, 3, self.heads, C // self.heads).permute(2, 0, 3, 1, 4)
-        o = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(-1, w * w, C)
-        o = self.proj(o).view(B, nw, nw, w, w, C).permute(0, 1, 3, 2, 4, 5).reshape(B, hw, hw, C)
-        if self.shift and w < hw:
+        n, hd = w * w, C // self.heads
+        x = x.view(B, nw, w, nw, w, C).permute(0, 1, 3, 2, 4, 5).reshape(B, nw * nw, n, C)
+        # [3, B, windows, heads, n, hd]; the windows of an image become extra heads so that one mask of
+        # [1, windows * heads, n, n] (or [1, heads, n, n] without a shift) broadcasts over the batch
+        qkv = self.qkv(x).view(B, nw * nw, n, 3, self.heads, hd).permute(3, 0, 1, 4, 2, 5)
+        mask = self.additive_mask(hw, w, x.dtype, x.device)
+        if shifted:
+            q, k, v = (t.reshape(B, nw * nw * self.heads, n, hd) for t in qkv)
+        else:
+            q, k, v = (t.reshape(B * nw * nw, self.heads, n, hd) for t in qkv)
+        o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+        o = o.view(B, nw * nw, self.heads, n, hd).transpose(2, 3).reshape(B, nw, nw, w, w, C)
+        o = self.proj(o).permute(0, 1, 3, 2, 4, 5).reshape(B, hw, hw, C)
+        if shifted:
             o = torch.roll(o, shifts=(self.shift, self.shift), dims=(1, 2))
         return o.reshape(B, N, C)
 

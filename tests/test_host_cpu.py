@@ -170,3 +170,49 @@ def test_fused_gate_step_declines_what_it_cannot_do():
     assert fused_topk_gshard(logits, 2, ops) is None
     assert fused_topk_gshard(logits.to(torch.bfloat16), 2, ops) is None
     assert fused_topk_gshard(logits, 2, None) is None
+
+
+def test_barrier_watchdog_releases_and_reports_after_its_deadline():
+    """Host logic of the bounded rank barrier, with a fake clock and fake probes (no GPU, no sleeping): a probe that
+    completes is forgotten; one that stays unfinished past the deadline trips the watchdog exactly once, the release
+    action runs, and the cache raises at its next use instead of waiting for a rank that is gone."""
+    from hexa_moe_b200._lib import HexaError
+    from hexa_moe_b200.impls.param_cache import BarrierWatchdog, PipelineSharedCache
+    now = [0.0]
+    released = []
+    wd = BarrierWatchdog(timeout_s=5.0, release=lambda: released.append(now[0]), clock=lambda: now[0], poll_s=3600.0)
+    state = {"a": False}
+    wd.watch(lambda: state["a"], "barrier A")
+    wd.watch(lambda: False, "barrier B (its peer never arrives)")
+    assert wd.pending() == 2 and not wd.poll_once()
+    now[0] = 4.0
+    state["a"] = True
+    assert not wd.poll_once() and wd.pending() == 1          # A done; B still inside its deadline
+    now[0] = 5.5
+    assert wd.poll_once() and released == [5.5]
+    assert "barrier B" in wd.failed and wd.pending() == 0
+    assert wd.poll_once() and released == [5.5]              # trips once
+    wd.stop()
+
+    class Owner:           # the few attributes the cache reads before it would touch a device
+        world_size, total_depth_moe = 2, 1
+    cache = PipelineSharedCache(Owner())
+    cache._watchdog = wd
+    with pytest.raises(HexaError, match="HEXA_BARRIER_TIMEOUT_S"):
+        cache.prefetch(0)
+    with pytest.raises(HexaError, match="peer has failed or left"):
+        cache.reduce_deferred(0, "fc1", None, None, [1, 1], 0)
+    cache.close()                                            # does not block on anything after a failure
+
+
+def test_barrier_watchdog_thread_trips_on_a_real_clock():
+    import time
+    from hexa_moe_b200.impls.param_cache import BarrierWatchdog
+    hit = []
+    wd = BarrierWatchdog(timeout_s=0.2, release=lambda: hit.append(1), poll_s=0.02)
+    wd.watch(lambda: False, "barrier whose peer left between steps")
+    t0 = time.monotonic()
+    while not hit and time.monotonic() - t0 < 5.0:
+        time.sleep(0.02)
+    assert hit == [1] and "left between steps" in wd.failed and time.monotonic() - t0 < 5.0
+    wd.stop()

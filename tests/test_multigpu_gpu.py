@@ -110,9 +110,13 @@ def _run(data_centric, proportion, dtype_name):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, data_centric, proportion, dtype_name, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=300) for _ in range(2)]
-    for p in procs:
-        p.join(60)
+    try:
+        res = [q.get(timeout=300) for _ in range(2)]
+    finally:
+        for p in procs:
+            p.join(60)
+            if p.is_alive():          # a rank that is stuck must not keep its GPU behind the test
+                p.kill()
     for rank, msg in res:
         assert msg == "ok", f"rank {rank}: {msg}"
 

@@ -31,9 +31,9 @@ def _full_params(E, d, H, n_layers, seed=0):
     return P
 
 
-def _worker(rank, world, port, data_centric, proportion, tokens_per_rank, q):
+def _worker(rank, world, port, data_centric, proportion, tokens_per_rank, q, defer_grads="1"):
     sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), HEXA_DEFER_GRADS=defer_grads)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         import oracle_backend
@@ -61,7 +61,17 @@ def _worker(rank, world, port, data_centric, proportion, tokens_per_rank, q):
         for i in range(L):
             h, l = m(i, h)
             aux = aux + l
-        h.sum().backward()
+        if defer_grads == "0":
+            # the reduced expert gradients come back through autograd itself: torch.autograd.grad sees them
+            prms = [m.batched_fc1_w[0], m.batched_fc2_w[0], m.batched_fc1_bias[0], m.batched_fc2_bias[0],
+                    m.batched_fc1_w[1], m.batched_fc2_w[1], m.batched_fc1_bias[1], m.batched_fc2_bias[1]]
+            grads = torch.autograd.grad(h.sum(), [x] + prms)
+            x.grad = grads[0]
+            for p_, g_ in zip(prms, grads[1:]):
+                assert g_ is not None and g_.shape == p_.shape
+                p_.grad = g_
+        else:
+            h.sum().backward()
 
         # expectation from the oracle, layer by layer on every rank's tokens
         def run_rank(r):
@@ -101,17 +111,22 @@ def _worker(rank, world, port, data_centric, proportion, tokens_per_rank, q):
         dist.destroy_process_group()
 
 
-def _run(data_centric, proportion, tokens_per_rank):
+def _run(data_centric, proportion, tokens_per_rank, defer_grads="1"):
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, data_centric, proportion, tokens_per_rank, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, data_centric, proportion, tokens_per_rank, q, defer_grads))
+             for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=240) for _ in range(world)]
-    for p in procs:
-        p.join(60)
+    try:
+        res = [q.get(timeout=240) for _ in range(world)]
+    finally:
+        for p in procs:
+            p.join(60)
+            if p.is_alive():          # a rank that is stuck must not outlive the test
+                p.kill()
     for rank, msg in res:
         assert msg == "ok", f"rank {rank}: {msg}"
 
@@ -124,6 +139,13 @@ def test_data_centric_two_ranks(proportion):
 @pytest.mark.parametrize("proportion,tokens", [(None, [32, 32]), ([0.3, 0.7], [24, 40])])
 def test_model_centric_two_ranks(proportion, tokens):
     _run(False, proportion, tokens)
+
+
+@pytest.mark.parametrize("proportion", [None, [0.7, 0.3]])
+def test_data_centric_gradients_through_autograd_when_not_deferred(proportion):
+    """HEXA_DEFER_GRADS=0: backward returns the reduced slices like the reference does (impls/layers.py:431-474)
+    instead of adding them to .grad from an end-of-backward callback."""
+    _run(True, proportion, [40, 40], defer_grads="0")
 
 
 def _ckpt_worker(rank, world, port, proportion, q):
