@@ -68,12 +68,16 @@ def parse():
     return ap.parse_args()
 
 
+TRAFFIC_RATIO = 1.0      # dram bytes per launch / algorithmic bytes per launch of the GEMM kernels, from the ncu capture
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return dict(tflops=float(p.get("bf16_tflops_sustained", p.get("bf16_tflops"))), hbm=float(p["hbm_gbs"]), source="measured")
-    return dict(tflops=1400.0, hbm=6650.0, source="fallback")
+        return dict(tflops=float(p.get("bf16_tflops_sustained", p.get("bf16_tflops"))), burst=float(p["bf16_tflops"]),
+                    hbm=float(p["hbm_gbs"]), source="measured")
+    return dict(tflops=1400.0, burst=1590.0, hbm=6650.0, source="fallback")
 
 
 class InputPrefetcher:
@@ -176,13 +180,20 @@ def cpu_pass(data):
     return time.perf_counter() - t0
 
 
-def cpu_sample_size(d, H, k, budget_s=15.0):
-    """Tokens that make one CPU pass last about budget_s, from a short probe."""
-    probe = cpu_setup(d, H, 8, k, 2048)
-    cpu_pass(probe)
-    rate = 2048 / cpu_pass(probe)
-    n = int(rate * budget_s)
-    return max(2048, min(n // 1024 * 1024, 65536))
+CPU_SAMPLE_TOKENS, CPU_SAMPLE_EXPERTS = 16384, 8
+
+
+def cpu_sample(d, H, k):
+    """The CPU arm's bounded sample, the same on every box: 16384 tokens (seed 0) routed top-k over 8 experts of the
+    layer's own d and hidden size.  Per-token work (12*k*d*H flop forward + backward) is that of the full layer and
+    does not depend on the expert count, so tokens/s of the sample is the rate of the full layer; nothing is
+    extrapolated."""
+    return cpu_setup(d, H, CPU_SAMPLE_EXPERTS, k, CPU_SAMPLE_TOKENS)
+
+
+def cpu_sample_text(k, E):
+    return (f"{CPU_SAMPLE_TOKENS} tokens (seed 0) top-{k} over {CPU_SAMPLE_EXPERTS} of the {E} experts, same d / hidden and "
+            f"per-token work as the full layer, fp32, all host cores")
 
 
 def run_reference(args):
@@ -197,21 +208,20 @@ def run_reference(args):
         return
     d, H, EXPERTS, _ = WORKLOADS[args.workload]
     k = TOP_K
-    E_s = 8
-    n = cpu_sample_size(d, H, k, budget_s=8.0)
-    data = cpu_setup(d, H, E_s, k, n)
+    n = CPU_SAMPLE_TOKENS
+    data = cpu_sample(d, H, k)
     for _ in range(min(args.warmup, 1)):
         cpu_pass(data)
     dt = sum(cpu_pass(data) for _ in range(args.steps)) / args.steps
     val = n / dt
     cores = os.cpu_count() or 1
-    sample = f"{n} tokens top-{k} over {E_s} of the {EXPERTS} experts per step (same d, hidden, per-token work), fp32"
+    sample = cpu_sample_text(k, EXPERTS) + ", one fwd+bwd pass per step"
     line = dict(metric="moe_layer_fwd_bwd_tokens_per_s", value=val, unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
                 warmup=args.warmup, ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None,
                 dtype="f32", data="synthetic", impl="reference",
                 config=dict(workload=args.workload + "-layer", d_model=d, hidden=H, experts=EXPERTS,
                             top_k=k, note="CPU oracle port: the reference ships no CPU path for these operators"),
-                cpu_baseline=dict(value=val, unit="tokens/s", cores=cores, kind="port", sample=sample),
+                cpu_baseline=dict(value=val, unit="tokens/s", cores=cores, kind="port", sample=sample, extrapolated=False),
                 e2e=dict(value=val, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
 
@@ -368,6 +378,7 @@ def run_swin(args, dev, rank, world, timed_factory=None):
     clocks = sampler.stop() if sampler else None
     step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
+    parity = multi_gpu_parity(rank, world, dev, True, None) if world > 1 else None
     if rank == 0:
         moe_tokens = sum(m.moe_tokens_per_image()) * args.images * world
         line = dict(metric="swin_moe_images_per_s", value=args.images * world / (ms * 1e-3), unit="images/s", n_gpus=world,
@@ -375,8 +386,9 @@ def run_swin(args, dev, rank, world, timed_factory=None):
                     vs_baseline=None, dtype="bf16", data="synthetic",
                     config=dict(workload="c4-swin-moe-b-like", images_per_gpu=args.images, img=192, experts=32, top_k=1,
                                 moe_layers=len(m.moe_idx), mode="data-centric",
-                                note="window attention without shift mask / relative position bias (timing harness)"),
-                    moe_layer_tokens_per_s=moe_tokens / (ms * 1e-3),
+                                note="window attention with relative position bias and shifted-window mask; stock PyTorch "
+                                     "attention blocks around one shared MoE_Cascaded"),
+                    moe_layer_tokens_per_s=moe_tokens / (ms * 1e-3), parity=parity,
                     e2e=dict(value=args.images * world / (ms_e2e * 1e-3), unit="images/s", ms_per_step=ms_e2e,
                              h2d_bytes_per_step=imgs_host.numel() * 2, d2h_bytes_per_step=4),
                     gpu_launches=launches, clocks=clocks)
@@ -386,6 +398,140 @@ def run_swin(args, dev, rank, world, timed_factory=None):
         m.cascaded_moe.dispatch_params.cache.close()
         dist.barrier()
         dist.destroy_process_group()
+
+
+def mean_square(h):
+    """mean(h^2) in fp32 as one reduction pass forward and one scaling pass backward (the unfused
+    h.float().pow(2).mean() makes seven passes over an activation-sized tensor; the loss of the benchmark step should
+    cost what a fused loss costs)."""
+    import torch
+
+    class _MeanSquare(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, t):
+            ctx.save_for_backward(t)
+            return torch.linalg.vector_norm(t, dtype=torch.float32).square() / t.numel()
+
+        @staticmethod
+        def backward(ctx, g):
+            (t,) = ctx.saved_tensors
+            return t * (g * (2.0 / t.numel()))
+    return _MeanSquare.apply(h)
+
+
+# ------------------------------------------------------------------------------------------------
+# multi-GPU correctness and timeline, outside every timed region
+# ------------------------------------------------------------------------------------------------
+def multi_gpu_parity(rank, world, dev, data_centric, proportion, dtype_name="bfloat16"):
+    """One small fixed-seed forward + backward of a two-layer module on all ranks (6 experts, d=64, hidden 256,
+    384 tokens per rank, top-2), compared with the CPU oracle's float64 layer: output, input gradient and the four
+    parameter gradients of both layers on every rank.  The oracle is the checker only.  Returns a dict for the JSON
+    line; `ok` is the AND over ranks, `max_rel` the largest error over ranks relative to the tolerance's scale."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from hexa_moe import moe as hmoe
+    from oracle import hexa_oracle as O
+    dtype = getattr(torch, dtype_name)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    E, d, H, k, L, T = 6, 64, 256, 2, 2, 384
+    m = hmoe.MoE_Cascaded(gate_type={'type': 'top', 'k': k, 'fp32_gate': True}, model_dim_list=[d] * L, moe_idx_list=[0, 1],
+                          mlp_ratio=H // d, mlp_proportion=proportion, num_global_experts=E, total_depth=L,
+                          data_centric=data_centric, activation_fn=lambda t: F.gelu(t))
+    g = torch.Generator().manual_seed(0)
+    P = [dict(w1=torch.randn(E, H, d, generator=g) * 0.15, w2=torch.randn(E, H, d, generator=g) * 0.1,
+              b1=torch.randn(E, H, generator=g) * 0.1, b2=torch.randn(E, d, generator=g) * 0.1,
+              wg=torch.randn(E, d, generator=g) * 0.5) for _ in range(L)]
+    split = [m.local_dim_list_all[r][0] for r in range(world)]
+    lo, n = sum(split[:rank]), split[rank]
+    with torch.no_grad():
+        for i in range(L):
+            for prm in (m.batched_fc1_w[i], m.batched_fc2_w[i], m.batched_fc1_bias[i]):
+                prm.zero_()
+            m.batched_fc1_w[i][:, :n] = P[i]["w1"][:, lo: lo + n]
+            m.batched_fc2_w[i][:, :n] = P[i]["w2"][:, lo: lo + n]
+            m.batched_fc1_bias[i][:, :n] = P[i]["b1"][:, lo: lo + n]
+            m.batched_fc2_bias[i].copy_(P[i]["b2"]); m.gates[i].wg.weight.copy_(P[i]["wg"])
+    m = m.to(dtype).to(dev).eval()
+    Pd = [{k_: v.to(dtype).float() for k_, v in p.items()} for p in P]      # what the module really holds
+    xs = [torch.randn(T, d, generator=torch.Generator().manual_seed(100 + r)).to(dtype) for r in range(world)]
+    x = xs[rank].to(dev).requires_grad_(True)
+    ids_used, h = [], x
+    for i in range(L):
+        h, _ = m(i, h)
+        ids_used.append(torch.stack([t.cpu() for t in m.dispatch_params.indices_], dim=1))
+    h.float().sum().backward()
+    torch.cuda.synchronize()
+    all_ids = [[None] * world for _ in range(L)]
+    for i in range(L):
+        dist.all_gather_object(all_ids[i], ids_used[i])
+
+    def run_rank(r):
+        cur, saved = xs[r].double(), []
+        for i in range(L):
+            res = O.moe_layer(cur, all_ids[i][r], Pd[i]["w1"], Pd[i]["w2"], Pd[i]["b1"], Pd[i]["b2"], F.gelu)
+            saved.append((cur, all_ids[i][r])); cur = res["y"].to(dtype).double()
+        gy, grads = torch.ones_like(cur), [None] * L
+        for i in reversed(range(L)):
+            cin, ids = saved[i]
+            grads[i] = O.moe_layer(cin, ids, Pd[i]["w1"], Pd[i]["w2"], Pd[i]["b1"], Pd[i]["b2"], F.gelu, gy)
+            gy = grads[i]["dx"].to(dtype).double()
+        return cur, gy, grads
+    outs = [run_rank(r) for r in range(world)]
+
+    def err(a, b):
+        a, b = a.detach().double().cpu(), b.double()
+        return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+    worst = max(err(h, outs[rank][0]), err(x.grad, outs[rank][1]))
+    for i in range(L):
+        comb = (lambda key: sum(outs[r][2][i][key] for r in range(world)) / world) if data_centric else \
+               (lambda key: sum(outs[r][2][i][key] for r in range(world)))
+        for prm, key, sliced in ((m.batched_fc1_w[i], "dw1", True), (m.batched_fc2_w[i], "dw2", True),
+                                 (m.batched_fc1_bias[i], "db1", True), (m.batched_fc2_bias[i], "db2", False)):
+            want = comb(key)[:, lo: lo + n] if sliced else comb(key)
+            got = prm.grad[:, :n] if sliced else prm.grad
+            worst = max(worst, err(got, want) / 1.5)          # reduced gradients: 1.5 x the tolerance, as in tests/
+    if m.dispatch_params.cache is not None:
+        dist.barrier(); m.dispatch_params.cache.close(); dist.barrier()
+    t = torch.tensor([worst], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    worst = float(t)
+    return dict(ok=bool(worst < tol), max_rel=worst, tolerance=tol, dtype=dtype_name, ranks=world,
+                mode="data-centric" if data_centric else "model-centric", hidden_split=split,
+                checked="y, dx, dW1, dW2, db1, db2 of both layers on every rank against the float64 CPU oracle; "
+                        "6 experts, d=64, hidden 256, 384 tokens per rank, top-2")
+
+
+def scale_timeline(cache, step_fn, steps, dev, world, my_kernel_ms, ms_step):
+    """Where a multi-GPU step spends time outside this library's kernels: spans recorded by the pipeline-shared cache
+    around every wait of the compute stream and every action of the side stream during `steps` extra steps, plus
+    the spread over ranks of the kernel time per step (the slowest rank paces a synchronous step)."""
+    import torch
+    import torch.distributed as dist
+    cache.timeline = []
+    dist.barrier()
+    torch.cuda.synchronize()
+    for _ in range(steps):
+        step_fn()
+    torch.cuda.synchronize()
+    spans, cache.timeline = cache.timeline, None
+    agg = {}
+    for site, stream_name, a, b in spans:
+        key = stream_name + ":" + site
+        agg[key] = agg.get(key, 0.0) + a.elapsed_time(b) / steps
+    everyone = [None] * world
+    dist.all_gather_object(everyone, dict(spans=agg, kernel_ms=my_kernel_ms))
+    sites = sorted({k for e in everyone for k in e["spans"]})
+    table = {}
+    for k in sites:
+        v = [e["spans"].get(k, 0.0) for e in everyone]
+        table[k] = dict(min=round(min(v), 3), mean=round(sum(v) / len(v), 3), max=round(max(v), 3))
+    km = [e["kernel_ms"] for e in everyone]
+    exposed = [sum(v for k, v in e["spans"].items() if k.startswith("compute:")) for e in everyone]
+    return dict(unit="ms per step", steps=steps, ms_per_step=round(ms_step, 3),
+                kernel_ms_by_rank=[round(v, 2) for v in km], exposed_wait_ms_by_rank=[round(v, 3) for v in exposed],
+                note="compute:* = time the compute stream was held at that wait; side:* = duration on the side stream "
+                     "(overlapped with compute unless a compute wait shows it)", sites=table)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -471,7 +617,7 @@ def main():
         for i in range(L):
             h, l = m(i, h)
             aux = aux + l
-        loss = h.float().pow(2).mean() + 0.01 * aux
+        loss = mean_square(h) + 0.01 * aux
         loss.backward()
         return loss
 
@@ -524,11 +670,14 @@ def main():
     ms_e2e = timed(step_e2e, args.steps)
 
     # ---- per-kernel summary from the events recorded during the timed steps ----
-    per = {}
+    per, per_type = {}, {}
     for name, e0, e1, work, nbytes in prof:
         t_ms = e0.elapsed_time(e1)
         s = per.setdefault(name.split(":")[0], [0, 0.0, 0.0, 0.0])
         s[0] += 1; s[1] += t_ms; s[2] += work; s[3] += nbytes
+        if name.startswith(("esmm:", "estmm:")):
+            s = per_type.setdefault(name, [0, 0.0, 0.0, 0.0])
+            s[0] += 1; s[1] += t_ms; s[2] += work; s[3] += nbytes
     pk = peaks()
     z = [0, 0.0, 0.0, 0.0]
     gemm_n = per.get("esmm", z)[0] + per.get("estmm", z)[0]
@@ -536,15 +685,32 @@ def main():
     gemm_fl = per.get("esmm", z)[2] + per.get("estmm", z)[2]
     gemm_by = per.get("esmm", z)[3] + per.get("estmm", z)[3]
     achieved = gemm_fl / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    # DRAM bytes per launch: ncu captures of these kernels (dram read + write per launch against the algorithmic
+    # operand + output bytes, one launch of each type) give the ratio; the headline workload itself is too large to
+    # capture, so `traffic` is the algorithmic bytes of the timed launches times that measured ratio
+    ratio = TRAFFIC_RATIO
+    by_type = {n_: dict(launches=v[0], avg_ms=round(v[1] / v[0], 4), tflops=round(v[2] / (v[1] * 1e-3) / 1e12, 1),
+                        frac_of_sustained=round(v[2] / (v[1] * 1e-3) / 1e12 / pk["tflops"], 3),
+                        frac_of_burst=round(v[2] / (v[1] * 1e-3) / 1e12 / pk["burst"], 3))
+               for n_, v in sorted(per_type.items()) if v[1] > 0}
     roofline = dict(bound="tensor", kernel="gemm_tc_kernel (ESMM + ESTMM launches)", achieved=achieved, peak=pk["tflops"],
                     unit="TFLOP/s", frac=achieved / pk["tflops"], peak_source=pk["source"] + " (sustained cuBLAS bf16)",
+                    frac_of_burst=achieved / pk["burst"], burst_peak=pk["burst"],
                     launches=gemm_n, avg_launch_ms=gemm_ms / max(gemm_n, 1), flops_per_launch=gemm_fl / max(gemm_n, 1),
-                    # DRAM bytes per launch: the ncu capture of these kernels on the c2 workload measured
-                    # dram read+write = 0.95-1.05 x the algorithmic operand+output bytes for every instantiation
-                    # (profiles/gemm_tc_kernel_c2-layer.md); the headline workload is too large to capture, so the
-                    # figure here is the algorithmic bytes of the timed launches scaled by that ratio (1.0)
-                    traffic=gemm_by / max(gemm_n, 1), traffic_source="ncu c2 capture, scaled by algorithmic bytes")
+                    traffic=ratio * gemm_by / max(gemm_n, 1),
+                    traffic_source="algorithmic bytes x %.2f (dram bytes / algorithmic bytes of an ncu capture at the "
+                                   "headline d / hidden with 8 experts)" % ratio,
+                    by_launch_type=by_type)
     kernels = {n_: dict(calls=v[0], ms_total=round(v[1], 3)) for n_, v in per.items()}
+    my_kernel_ms = sum(v[1] for v in per.values()) / args.steps
+
+    parity, timeline = None, None
+    if world > 1:
+        cache = m.dispatch_params.cache
+        if cache is not None and cache.side is not None:
+            timeline = scale_timeline(cache, step_resident, 3, dev, world, my_kernel_ms, ms)
+        dist.barrier()
+        parity = multi_gpu_parity(rank, world, dev, args.mode == "data", proportion)
 
     tokens_per_step = T * n_gpus * L
     value = tokens_per_step / (ms * 1e-3)
@@ -552,11 +718,12 @@ def main():
     layer_flops = 12.0 * T * k * d * H * L
     cpu_baseline = None
     if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
-        n_s = cpu_sample_size(d, H, k, budget_s=15.0)
-        secs = cpu_pass(cpu_setup(d, H, 8, k, n_s))
-        rate = n_s / secs
-        cpu_baseline = dict(value=rate, unit="tokens/s", cores=os.cpu_count() or 1, kind="port", seconds=round(secs, 2),
-                            sample=f"{n_s} tokens top-{k} over 8 of the {E} experts (same d, hidden and per-token work), fp32, one pass")
+        data = cpu_sample(d, H, k)
+        cpu_pass(data)                                               # warm-up (thread pool, page faults)
+        secs = sorted(cpu_pass(data) for _ in range(3))[1]           # median of three
+        cpu_baseline = dict(value=CPU_SAMPLE_TOKENS / secs, unit="tokens/s", cores=os.cpu_count() or 1, kind="port",
+                            seconds=round(secs, 2), sample=cpu_sample_text(k, E) + ", median of 3 passes after 1 warm-up",
+                            extrapolated=False)
     if rank == 0:
         line = dict(metric="moe_layer_fwd_bwd_tokens_per_s", value=value, unit="tokens/s", n_gpus=n_gpus, steps=args.steps,
                     warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True,
@@ -565,8 +732,11 @@ def main():
                                 top_k=k, layers=L, tokens_per_gpu=T, activation="gelu", mode=args.mode + "-centric",
                                 l2="inputs larger than L2 (expert weights %.1f GB per layer)" % (2 * E * H * d * 2 / 1e9)),
                     model_tflops_per_gpu=layer_flops / (ms * 1e-3) / 1e12,
+                    model_frac_of_burst=layer_flops / (ms * 1e-3) / 1e12 / pk["burst"],
                     e2e=dict(value=e2e_value, unit="tokens/s", ms_per_step=ms_e2e, h2d_bytes_per_step=x_host.numel() * 2,
-                             d2h_bytes_per_step=4),
+                             d2h_bytes_per_step=4, result="the loss scalar is read back every step; gradients stay on the "
+                                                          "device, where an optimizer would consume them"),
+                    parity=parity, scale_timeline=timeline,
                     gpu_launches=launches, kernels=kernels, roofline=roofline, cpu_baseline=cpu_baseline, clocks=clocks)
         print(json.dumps(line), flush=True)
     if world > 1:

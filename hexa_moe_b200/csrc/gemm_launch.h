@@ -17,5 +17,7 @@ int esmm_tc_launch(const void*, int64_t, const void*, int, int64_t, int64_t, con
                    int, int, cudaStream_t);
 bool estmm_tc_supported(const void*, int64_t, const void*, int64_t, const void*, int64_t, int64_t, int64_t, int64_t, int, int);
 int estmm_tc_launch(const void*, int64_t, const void*, int64_t, const int32_t*, int, int64_t, int64_t, int64_t, void*, int64_t,
-                    int64_t, int64_t, int64_t, int, int, int, cudaStream_t, void* const* split_out = nullptr, int n_split = 0);
+                    int64_t, int64_t, int64_t, int, int, int, cudaStream_t, void* const* split_out = nullptr, int n_split = 0,
+                    void* workspace = nullptr, size_t workspace_bytes = 0);
+size_t estmm_tc_workspace_bytes(int E, int64_t row_cap, int64_t m, int64_t n);
 }  // namespace hexa

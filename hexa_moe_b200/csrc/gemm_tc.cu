@@ -70,6 +70,8 @@ struct Params {
   int is_bf16;      // 16-bit flavour of the inputs (and of 16-bit outputs)
   int out_f32;      // ESTMM: fp32 output
   int beta;         // ESTMM: accumulate into out
+  int splits;       // ESTMM: > 1 = every expert's row segment is cut into this many chunks, each its own tile, whose fp32
+  float* partial;   //        partial results [splits, E, m, n] go here and are added in chunk order by estmm_reduce_kernel
   int debug;        // measurement / test aid (HEXA_TC_DEBUG, hexa_set_tc_debug): bit 0 = the producer skips the TMA loads and
                     // arrives in their place, bit 1 = the MMA thread skips the MMAs, bit 2 = the producer neither loads
                     // nor arrives, so that every wait of the pipeline runs into its limit
@@ -313,6 +315,7 @@ struct Tile {
   int m0;         // ESTMM: first output row of this CTA's block
   int num_kb;     // k-blocks to accumulate
   int valid;      // this CTA has rows to store (the second CTA of a pair may not)
+  int split;      // ESTMM with splits > 1: which chunk of the segment this tile covers
 };
 
 // Tile t of the static list, as seen by CTA `rank` of its pair (rank = 0 when CTAS = 1).  Returns false past the end.
@@ -320,14 +323,21 @@ template <int BN, int MODE, int CTAS>
 __device__ __forceinline__ bool get_tile(const Params& p, int64_t t, int rank, Tile& tile) {
   if (MODE == ESTMM) {
     const int64_t MT = (p.m + BLOCK_M * CTAS - 1) / (BLOCK_M * CTAS), NT = (p.n + BN - 1) / BN;
-    if (t >= (int64_t)p.E * MT * NT) return false;
-    const int e = (int)(t / (MT * NT));
-    const int64_t rem = t - (int64_t)e * MT * NT;
+    const int64_t S = p.splits;
+    if (t >= (int64_t)p.E * MT * NT * S) return false;
+    const int e = (int)(t / (MT * NT * S));
+    const int64_t rem = (t - (int64_t)e * MT * NT * S) / S;
+    const int c = (int)(t % S);
     tile.e = e;
     tile.m0 = ((int)(rem / NT) * CTAS + rank) * BLOCK_M;
     tile.col0 = (int)(rem % NT) * BN;
-    tile.row0 = p.pad_offsets[e];
-    tile.num_kb = (p.pad_offsets[e + 1] - tile.row0) / BLOCK_K;
+    const int seg0 = p.pad_offsets[e];
+    const int kb_all = (p.pad_offsets[e + 1] - seg0) / BLOCK_K;
+    const int kb_per = (int)((kb_all + S - 1) / S);          // chunks of equal length, the last ones may be short or empty
+    const int kb0 = c * kb_per;
+    tile.row0 = seg0 + kb0 * BLOCK_K;
+    tile.num_kb = max(0, min(kb_per, kb_all - kb0));
+    tile.split = c;
     tile.valid = tile.m0 < p.m;
     return true;
   } else {
@@ -612,7 +622,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int i = 0; i < 32; ++i) v[i] = 0u;
           }
           const int64_t mrow = (int64_t)tile.m0 + rloc;
-          if (mrow < p.m) {
+          if (mrow < p.m && p.splits > 1) {
+            // a chunk's partial result: plain fp32 [splits, E, m, n]
+            float* o = p.partial + (((int64_t)tile.split * p.E + tile.e) * p.m + mrow) * p.n + gcol;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (gcol + g * 4 < p.n)
+                *reinterpret_cast<float4*>(o + g * 4) = make_float4(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1]),
+                                                                    __uint_as_float(v[4 * g + 2]), __uint_as_float(v[4 * g + 3]));
+            }
+          } else if (mrow < p.m) {
             if (p.out_f32) {
               float* o = (p.n_split ? reinterpret_cast<float*>(p.c_split[mrow / p.m_split])
                                     : reinterpret_cast<float*>(p.c) + (mrow / p.m_split) * p.split_stride) +
@@ -741,6 +760,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc_fence_after();
     if (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
     else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
+  }
+}
+
+// Second pass of a split ESTMM: out = beta * out + sum over chunks (in chunk order) of the fp32 partial results, stored
+// in the output's own type and layout.  One thread per four adjacent columns.
+__global__ void __launch_bounds__(256)
+estmm_reduce_kernel(const float* __restrict__ partial, int splits, int E, int64_t m, int64_t n, void* __restrict__ out, int64_t ldc,
+                    int64_t c_estride, int64_t m_split, int64_t split_stride, int out_f32, int is_bf16, int beta) {
+  const int64_t n4 = n / 4;
+  const int64_t total = (int64_t)E * m * n4;
+  const int64_t plane = (int64_t)E * m * n;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t c4 = i % n4, row = i / n4;          // row = e * m + mrow
+    const int64_t e = row / m, mrow = row - e * m;
+    const float* src = partial + row * n + c4 * 4;
+    float4 acc = *reinterpret_cast<const float4*>(src);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)s * plane);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const int64_t off = (mrow / m_split) * split_stride + e * c_estride + (mrow % m_split) * ldc + c4 * 4;
+    if (out_f32) {
+      float* o = reinterpret_cast<float*>(out) + off;
+      if (beta) { const float4 old = *reinterpret_cast<float4*>(o); acc.x += old.x; acc.y += old.y; acc.z += old.z; acc.w += old.w; }
+      *reinterpret_cast<float4*>(o) = acc;
+    } else {
+      uint16_t* o = reinterpret_cast<uint16_t*>(out) + off;
+      if (beta) {
+        const uint2 old = *reinterpret_cast<uint2*>(o);
+        acc.x += unpack_lo(old.x, is_bf16); acc.y += unpack_hi(old.x, is_bf16);
+        acc.z += unpack_lo(old.y, is_bf16); acc.w += unpack_hi(old.y, is_bf16);
+      }
+      *reinterpret_cast<uint2*>(o) = make_uint2(pack2(acc.x, acc.y, is_bf16), pack2(acc.z, acc.w, is_bf16));
+    }
   }
 }
 
@@ -922,13 +975,42 @@ bool estmm_tc_supported(const void* p, int64_t ldp, const void* q, int64_t ldq, 
   return true;
 }
 
+// How many chunks a split ESTMM cuts every expert's segment into (1 = no split).  Only static sizes enter: the tile
+// count without a split against the CTA pairs (or CTAs) of the device, and the average segment length, so that a chunk
+// keeps at least 8 k-blocks.  Few, long segments - the dense FFN's weight gradient (one "expert" owning every row), or a
+// handful of experts with a small d x H - would otherwise leave most SMs idle behind a few serial k-loops.
+int estmm_tc_splits(int E, int64_t row_cap, int64_t m, int64_t n) {
+  static int forced = -2;
+  if (forced == -2) forced = env_int("HEXA_ESTMM_SPLITS", -1);       // A/B switch: 1 = never split
+  if (n % 4) return 1;
+  const int BN = n > 128 ? 256 : 128;
+  const int ctas = (BN == 256 && m > BLOCK_M && pairs_enabled()) ? 2 : 1;
+  const int64_t tiles = (int64_t)E * ceil_div(m, BLOCK_M * ctas) * ceil_div(n, BN);
+  const int64_t slots = ctas == 2 ? sm_count() / 2 : sm_count();
+  const int64_t avg_kb = row_cap / BLOCK_K / E;
+  int64_t s = 1;
+  if (tiles < 2 * slots) s = ceil_div(2 * slots, tiles);
+  if (s > avg_kb / 8) s = avg_kb / 8;
+  if (forced > 0) s = forced;
+  if (s > 32) s = 32;
+  return s < 1 ? 1 : (int)s;
+}
+
+size_t estmm_tc_workspace_bytes(int E, int64_t row_cap, int64_t m, int64_t n) {
+  const int s = estmm_tc_splits(E, row_cap, m, n);
+  return s > 1 ? (size_t)s * (size_t)E * (size_t)m * (size_t)n * sizeof(float) : 0;
+}
+
 int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets, int E,
                     int64_t row_cap, int64_t m, int64_t n, void* out, int64_t ldo, int64_t o_estride, int64_t m_split,
                     int64_t split_stride, int dtype, int out_dtype, int beta, cudaStream_t stream, void* const* split_out,
-                    int n_split) {
+                    int n_split, void* workspace, size_t workspace_bytes) {
   const int is_bf16 = dtype == HEXA_BF16;
   const int BN = n > 128 ? 256 : 128;
   const int ctas = (BN == 256 && m > BLOCK_M && pairs_enabled()) ? 2 : 1;
+  int splits = n_split > 0 ? 1 : estmm_tc_splits(E, row_cap, m, n);
+  if (splits > 1 && (!workspace || workspace_bytes < (size_t)splits * E * m * n * sizeof(float) || !aligned16(workspace)))
+    splits = 1;      // without scratch the operator still runs, one tile per expert's whole segment
   CUtensorMap tmA, tmB;
   // the maps need at least one row even when no token was routed
   const uint64_t rows = row_cap > 0 ? (uint64_t)row_cap : 1;
@@ -952,12 +1034,22 @@ int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, con
   p.n_split = n_split;
   for (int i = 0; i < n_split && i < 16; ++i) p.c_split[i] = split_out[i];
   p.is_bf16 = is_bf16; p.out_f32 = out_dtype == HEXA_F32; p.beta = beta;
+  p.splits = splits; p.partial = static_cast<float*>(workspace);
   p.status = status_word(); p.debug = tc_debug_flags(); p.wait_limit_ns = wait_limit_ns();
-  const int64_t max_tiles = (int64_t)E * ceil_div(m, BLOCK_M * ctas) * ceil_div(n, BN);
+  const int64_t max_tiles = (int64_t)E * ceil_div(m, BLOCK_M * ctas) * ceil_div(n, BN) * splits;
   // ESTMM stores straight from registers; the two output maps are unused placeholders
-  if (ctas == 2) return launch<256, ESTMM, 2>(tmA, tmB, tmA, tmA, p, max_tiles, stream);
-  return BN == 256 ? launch<256, ESTMM, 1>(tmA, tmB, tmA, tmA, p, max_tiles, stream)
-                   : launch<128, ESTMM, 1>(tmA, tmB, tmA, tmA, p, max_tiles, stream);
+  int rc;
+  if (ctas == 2) rc = launch<256, ESTMM, 2>(tmA, tmB, tmA, tmA, p, max_tiles, stream);
+  else rc = BN == 256 ? launch<256, ESTMM, 1>(tmA, tmB, tmA, tmA, p, max_tiles, stream)
+                      : launch<128, ESTMM, 1>(tmA, tmB, tmA, tmA, p, max_tiles, stream);
+  if (rc != HEXA_OK || splits == 1) return rc;
+  const int64_t total = (int64_t)E * m * (n / 4);
+  int64_t blocks = ceil_div(total, 256);
+  if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
+  estmm_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.partial, splits, E, m, n, out, ldo, o_estride, p.m_split, p.split_stride,
+                                                          p.out_f32, is_bf16, beta);
+  HEXA_LAUNCH_CHECK("estmm_reduce_kernel");
+  return HEXA_OK;
 }
 
 }  // namespace hexa

@@ -76,9 +76,15 @@ extern "C" int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout
                           row_token, E, row_cap, n_out, k, dtype, epilogue, act, stream);
 }
 
+extern "C" size_t hexa_estmm_workspace_bytes(int E, int64_t row_cap, int64_t m, int64_t n, int dtype) {
+  if (E <= 0 || row_cap <= 0 || m <= 0 || n <= 0 || (dtype != HEXA_F16 && dtype != HEXA_BF16)) return 0;
+  return estmm_tc_workspace_bytes(E, row_cap, m, n);
+}
+
 extern "C" int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets, int E,
                           int64_t row_cap, int64_t m, int64_t n, void* out, int64_t ldo, int64_t o_estride, int64_t m_split,
-                          int64_t split_stride, int dtype, int out_dtype, int beta, int engine, void* stream_) {
+                          int64_t split_stride, int dtype, int out_dtype, int beta, int engine, void* workspace,
+                          size_t workspace_bytes, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   HEXA_REQUIRE(p && q && out && pad_offsets, "hexa_estmm: null pointer");
   HEXA_REQUIRE(E > 0 && row_cap >= 0 && row_cap % kRowTile == 0 && m > 0 && n > 0,
@@ -98,7 +104,7 @@ extern "C" int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq
   }
   if (engine != HEXA_ENGINE_SIMT && tc_ok)
     return estmm_tc_launch(p, ldp, q, ldq, pad_offsets, E, row_cap, m, n, out, ldo, o_estride, m_split, split_stride, dtype, out_dtype,
-                           beta, stream);
+                           beta, stream, nullptr, 0, workspace, workspace_bytes);
   return estmm_simt_launch(p, ldp, q, ldq, pad_offsets, E, m, n, out, ldo, o_estride, m_split, split_stride, dtype, out_dtype, beta,
                            stream);
 }

@@ -36,7 +36,10 @@ __global__ void gather_rows_kernel(const uint8_t* __restrict__ src, int64_t src_
 }
 
 // ---- combine: warp per token, fp32 accumulation over the k routes in fixed order --------------
-template <typename T>
+// K > 0: top_k known at compile time - the token's K row indices are read once, and the K row loads of a column
+// chunk are issued together before anything is added (the adds keep the order j = 0..K-1, so the result does not
+// depend on K being a template parameter).  K = 0: any top_k.
+template <typename T, int K>
 __global__ void combine_rows_kernel(const T* __restrict__ src, int64_t src_ld, const int32_t* __restrict__ token_row,
                                     int64_t num_tokens, int top_k, int64_t cols, T* __restrict__ dst, int64_t dst_ld) {
   constexpr int V = 16 / sizeof(T);
@@ -44,7 +47,37 @@ __global__ void combine_rows_kernel(const T* __restrict__ src, int64_t src_ld, c
   const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= num_tokens) return;
   const bool vec_ok = (cols % V == 0) && (src_ld % V == 0) && (dst_ld % V == 0);
-  if (vec_ok) {
+  if (K > 0 && vec_ok) {
+    const T* rows[K > 0 ? K : 1];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int32_t r = __ldg(token_row + t * K + j);
+      rows[j] = r >= 0 ? src + (int64_t)r * src_ld : nullptr;
+    }
+#pragma unroll 2
+    for (int64_t c = (int64_t)lane * V; c < cols; c += 32 * V) {
+      uint4 raw[K > 0 ? K : 1];
+#pragma unroll
+      for (int j = 0; j < K; ++j)
+        raw[j] = rows[j] ? __ldg(reinterpret_cast<const uint4*>(rows[j] + c)) : make_uint4(0, 0, 0, 0);
+      float acc[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        if (rows[j]) {      // an unrouted choice adds nothing (not even -0 + 0)
+          const T* v = reinterpret_cast<const T*>(&raw[j]);
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[i] += to_f32<T>(v[i]);
+        }
+      }
+      uint4 outv;
+      T* o = reinterpret_cast<T*>(&outv);
+#pragma unroll
+      for (int i = 0; i < V; ++i) o[i] = from_f32<T>(acc[i]);
+      *reinterpret_cast<uint4*>(dst + t * dst_ld + c) = outv;
+    }
+  } else if (vec_ok) {
     for (int64_t c = (int64_t)lane * V; c < cols; c += 32 * V) {
       float acc[V];
 #pragma unroll
@@ -73,6 +106,22 @@ __global__ void combine_rows_kernel(const T* __restrict__ src, int64_t src_ld, c
       dst[t * dst_ld + c] = from_f32<T>(acc);
     }
   }
+}
+
+template <typename T>
+void combine_launch(const void* src, int64_t src_ld, const int32_t* token_row, int64_t T_, int top_k, int64_t cols, void* dst,
+                    int64_t dst_ld, cudaStream_t stream) {
+  const int warps = 8;
+  const unsigned grid = (unsigned)ceil_div(T_, warps);
+#define HEXA_COMBINE(K_)                                                                                              \
+  combine_rows_kernel<T, K_><<<grid, warps * 32, 0, stream>>>((const T*)src, src_ld, token_row, T_, top_k, cols, (T*)dst, dst_ld)
+  switch (top_k) {
+    case 1: HEXA_COMBINE(1); break;
+    case 2: HEXA_COMBINE(2); break;
+    case 4: HEXA_COMBINE(4); break;
+    default: HEXA_COMBINE(0); break;
+  }
+#undef HEXA_COMBINE
 }
 
 // ---- mask: zero the pad rows of a sorted buffer -------------------------------------------------
@@ -180,21 +229,10 @@ extern "C" int hexa_combine_rows(const void* src, int64_t src_ld, const int32_t*
   HEXA_REQUIRE(src && token_row && dst, "hexa_combine_rows: null pointer");
   HEXA_REQUIRE(aligned16(src) && aligned16(dst), "hexa_combine_rows: pointers must be 16-byte aligned");
   if (T == 0) return HEXA_OK;
-  const int warps = 8;
-  const unsigned grid = (unsigned)ceil_div(T, warps);
   switch (dtype) {
-    case HEXA_F32:
-      combine_rows_kernel<float><<<grid, warps * 32, 0, stream>>>((const float*)src, src_ld, token_row, T, top_k, cols,
-                                                                  (float*)dst, dst_ld);
-      break;
-    case HEXA_F16:
-      combine_rows_kernel<__half><<<grid, warps * 32, 0, stream>>>((const __half*)src, src_ld, token_row, T, top_k, cols,
-                                                                   (__half*)dst, dst_ld);
-      break;
-    case HEXA_BF16:
-      combine_rows_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>((const __nv_bfloat16*)src, src_ld, token_row, T,
-                                                                          top_k, cols, (__nv_bfloat16*)dst, dst_ld);
-      break;
+    case HEXA_F32: combine_launch<float>(src, src_ld, token_row, T, top_k, cols, dst, dst_ld, stream); break;
+    case HEXA_F16: combine_launch<__half>(src, src_ld, token_row, T, top_k, cols, dst, dst_ld, stream); break;
+    case HEXA_BF16: combine_launch<__nv_bfloat16>(src, src_ld, token_row, T, top_k, cols, dst, dst_ld, stream); break;
     default: HEXA_REQUIRE(false, "hexa_combine_rows: bad dtype %d", dtype);
   }
   HEXA_LAUNCH_CHECK("combine_rows");

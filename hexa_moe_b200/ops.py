@@ -134,7 +134,7 @@ def combine_rows(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = No
 def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Optional[torch.Tensor] = None,
          epilogue: int = L.EPI_LINEAR, act: int = L.ACT_NONE, aux: Optional[torch.Tensor] = None,
          out: Optional[torch.Tensor] = None, engine: int = L.ENGINE_AUTO, n_out: Optional[int] = None,
-         k: Optional[int] = None) -> torch.Tensor:
+         k: Optional[int] = None, tag: Optional[str] = None) -> torch.Tensor:
     """c[row] = a[row] x b[expert(row)] with the fused epilogue.  b: [E, n_out, k] (B_NK) or [E, k, n_out] (B_KN);
     b may be a view with arbitrary expert / row strides (unit inner stride)."""
     if r.align % L.ROW_TILE:
@@ -156,7 +156,7 @@ def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Opti
     rows_ = r.num_tokens * r.top_k
     es_ = a.element_size()
     nbytes = es_ * (rows_ * k + r.num_experts * n_out * k + rows_ * n_out * (1 if epilogue == L.EPI_LINEAR else 2))
-    with _Timed("esmm:%d" % epilogue, 2.0 * rows_ * n_out * k, float(nbytes)):
+    with _Timed("esmm:" + (tag or "epilogue%d" % epilogue), 2.0 * rows_ * n_out * k, float(nbytes)):
         check(lib().hexa_esmm(ptr(a), _ld(a), ptr(b), b_layout, b.stride(1), b.stride(0), ptr(bias),
                               0 if bias is None else _ld(bias), ptr(aux), 0 if aux is None else _ld(aux), ptr(out), _ld(out),
                               ptr(r.tile_expert), ptr(r.pad_offsets), ptr(r.row_token), ptr(r.pair_block), r.num_experts, r.row_capacity,
@@ -166,7 +166,7 @@ def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Opti
 
 
 def estmm(p: torch.Tensor, q: torch.Tensor, r: Routing, out_dtype: Optional[torch.dtype] = None,
-          out=None, beta: int = 0, engine: int = L.ENGINE_AUTO, ranks: int = 1):
+          out=None, beta: int = 0, engine: int = L.ENGINE_AUTO, ranks: int = 1, tag: Optional[str] = None):
     """out[e] = p_e^T q_e over expert e's rows: [E, p.cols, q.cols].
     ranks > 1 (p.cols divisible by it): the result is laid out [ranks, E, p.cols/ranks, q.cols], i.e. already
     grouped by the rank that owns each slice of the hidden dimension (what a reduce-scatter consumes).  `out` may
@@ -189,7 +189,8 @@ def estmm(p: torch.Tensor, q: torch.Tensor, r: Routing, out_dtype: Optional[torc
             raise L.HexaError("estmm: per-owner outputs must be [E, rows/ranks, cols]")
         import ctypes as C
         ptrs = (C.c_void_p * ranks)(*[t.data_ptr() for t in out])
-        with _Timed("estmm", 2.0 * rows_ * m * n, float(p.element_size() * rows_ * (m + n) + o0.element_size() * r.num_experts * m * n)):
+        with _Timed("estmm:" + (tag or "dw"), 2.0 * rows_ * m * n,
+                    float(p.element_size() * rows_ * (m + n) + o0.element_size() * r.num_experts * m * n)):
             check(lib().hexa_estmm_scatter(ptr(p), _ld(p), ptr(q), _ld(q), ptr(r.pad_offsets), r.num_experts, r.row_capacity, m, n,
                                            ptrs, ranks, o0.stride(1), o0.stride(0), m // ranks, dt(p), dt(o0), stream_of(p)),
                   "hexa_estmm_scatter")
@@ -208,9 +209,13 @@ def estmm(p: torch.Tensor, q: torch.Tensor, r: Routing, out_dtype: Optional[torc
         ldo, estride, m_split, split_stride = out.stride(1), out.stride(0), 0, 0
     if out.stride(-1) != 1:
         raise L.HexaError("estmm: out must have unit inner stride")
-    with _Timed("estmm", 2.0 * rows_ * m * n, float(p.element_size() * rows_ * (m + n) + out.element_size() * r.num_experts * m * n)):
+    ws_bytes = lib().hexa_estmm_workspace_bytes(r.num_experts, r.row_capacity, m, n, dt(p)) if engine != L.ENGINE_SIMT else 0
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=p.device) if ws_bytes else None
+    with _Timed("estmm:" + (tag or "dw"), 2.0 * rows_ * m * n,
+                float(p.element_size() * rows_ * (m + n) + out.element_size() * r.num_experts * m * n)):
         check(lib().hexa_estmm(ptr(p), _ld(p), ptr(q), _ld(q), ptr(r.pad_offsets), r.num_experts, r.row_capacity, m, n, ptr(out),
-                               ldo, estride, m_split, split_stride, dt(p), dt(out), beta, engine, stream_of(p)), "hexa_estmm")
+                               ldo, estride, m_split, split_stride, dt(p), dt(out), beta, engine, ptr(ws), ws_bytes,
+                               stream_of(p)), "hexa_estmm")
     return out
 
 
@@ -332,9 +337,9 @@ def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=Fa
     y1 = sorted_buffer(r.row_capacity, H, x.dtype, x.device)
     g = None
     if act_id >= 0:
-        h = esmm(xs, w1, L.B_NK, r, b1f, L.EPI_ACT, act_id, aux=y1, engine=engine)
+        h = esmm(xs, w1, L.B_NK, r, b1f, L.EPI_ACT, act_id, aux=y1, engine=engine, tag="fc1_forward_act")
     else:
-        esmm(xs, w1, L.B_NK, r, b1f, L.EPI_LINEAR, out=y1, engine=engine)
+        esmm(xs, w1, L.B_NK, r, b1f, L.EPI_LINEAR, out=y1, engine=engine, tag="fc1_forward")
         if need_state:
             with torch.enable_grad():
                 yy = y1.detach().requires_grad_(True)
@@ -346,7 +351,7 @@ def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=Fa
         mask_pad_rows(h, r)
     if before_fc2 is not None:      # e.g. wait for w2 to finish arriving from the other ranks
         before_fc2()
-    ys = esmm(h, w2, L.B_KN, r, b2f, L.EPI_LINEAR, engine=engine)
+    ys = esmm(h, w2, L.B_KN, r, b2f, L.EPI_LINEAR, engine=engine, tag="fc2_forward")
     y = combine_rows(ys, r)
     return y, (LayerState(r, xs, y1, h, g) if need_state else None)
 
@@ -358,11 +363,11 @@ def moe_backward_fc2(st: LayerState, dy, w2, act_id: int, has_b2=True, grad_dtyp
     r = st.routing
     dys = gather_rows(dy.contiguous(), r)
     db2 = ess(dys, r) if has_b2 else None
-    dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine, ranks=ranks, out=dw_out)
+    dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine, ranks=ranks, out=dw_out, tag="dw2")
     if act_id >= 0:
-        dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_DACT, act_id, aux=st.y1, engine=engine)
+        dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_DACT, act_id, aux=st.y1, engine=engine, tag="fc2_dgrad_dact")
     else:
-        dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_LINEAR, engine=engine)
+        dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_LINEAR, engine=engine, tag="fc2_dgrad")
         dh.mul_(st.act_grad)
         mask_pad_rows(dh, r)
     return dh, dw2, db2
@@ -375,10 +380,10 @@ def moe_backward_fc1(st: LayerState, dh, w1, has_b1=True, grad_dtype=None, engin
     reducing them across ranks while that GEMM runs."""
     r = st.routing
     db1 = ess(dh, r) if has_b1 else None
-    dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine, ranks=ranks, out=dw_out)
+    dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine, ranks=ranks, out=dw_out, tag="dw1")
     if after_dw is not None:
         after_dw(dw1, db1)
-    dxs = esmm(dh, w1, L.B_KN, r, None, L.EPI_LINEAR, engine=engine)
+    dxs = esmm(dh, w1, L.B_KN, r, None, L.EPI_LINEAR, engine=engine, tag="fc1_dgrad")
     dx = combine_rows(dxs, r)
     return dx, dw1, db1
 

@@ -170,11 +170,19 @@ int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout, int64_t l
  *   out + e*o_estride + (i / m_split)*split_stride + (i % m_split)*ldo,
  * which lets the gradient land directly in the [ranks, E, m/ranks, n] layout a reduce-scatter over the
  * hidden dimension consumes (m_split = m/ranks, split_stride = E*m_split*ldo, o_estride = m_split*ldo).
- * Pass m_split = 0 for the plain [E, m, n] layout. */
+ * Pass m_split = 0 for the plain [E, m, n] layout.
+ * workspace (optional): when the output has few tiles and the segments are long - the weight gradient of a dense FFN
+ * run as one expert, or a few experts with a small m x n - one tile per expert's whole segment would leave most SMs
+ * idle.  With hexa_estmm_workspace_bytes(...) bytes of 16-byte aligned scratch the tcgen05 kernel cuts every segment
+ * into chunks (the count depends only on the static sizes), writes fp32 partial results there and adds them in chunk
+ * order in a second kernel: deterministic, same rounding of the final result.  The query returns 0 when no split
+ * would be used; NULL / too small a workspace runs the unsplit kernel.  (The reference accumulates a whole segment in
+ * one program, kernels/fused.py:183-235.) */
+size_t hexa_estmm_workspace_bytes(int num_experts, int64_t row_capacity, int64_t m, int64_t n, int dtype);
 int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets,
                int num_experts, int64_t row_capacity, int64_t m, int64_t n, void* out, int64_t ldo,
                int64_t o_estride, int64_t m_split, int64_t split_stride, int dtype, int out_dtype, int beta,
-               int engine, void* stream);
+               int engine, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ESTMM whose output slices go to separate buffers (no reference counterpart; the reference all-reduces the full
  * gradient through torch.distributed, impls/layers.py:431-474): output row i of expert e is written at

@@ -288,6 +288,43 @@ def test_estmm_tcgen05(ops, dtype, out_dtype, M, N):
     _estmm_case(ops, dtype, L().ENGINE_TCGEN05, T=2500, k=2, E=7, M=M, N=N, out_dtype=out_dtype, seed=M)
 
 
+@pytest.mark.parametrize("E,M,N,out_dtype,ranks", [(1, 256, 512, torch.float32, 1), (1, 512, 128, torch.bfloat16, 1),
+                                                    (3, 256, 256, torch.float32, 2), (2, 200, 136, torch.bfloat16, 1)])
+def test_estmm_split_segments(ops, E, M, N, out_dtype, ranks):
+    """Few output tiles and long segments (the dense FFN's weight gradient is the E = 1 case): with scratch the kernel
+    cuts every segment into chunks and adds the fp32 partial results in chunk order.  Same answer as the oracle and as
+    the unsplit kernel, bit-identical from run to run, beta and the rank-grouped layout honoured, an expert without
+    rows written as zeros."""
+    Lb = L()
+    T, k = 6000, 1
+    g = torch.Generator().manual_seed(E * 100 + M)
+    ids = torch.randint(0, max(E - 1, 1), (T, k), generator=g).to(torch.int32)          # the last of several experts stays empty
+    r = ops.route(ids.cuda(), E)
+    p = torch.randn(T, M, generator=g).bfloat16(); q = torch.randn(T, N, generator=g).bfloat16()
+    ps, qs = ops.gather_rows(p.cuda(), r), ops.gather_rows(q.cuda(), r)
+    lib = Lb.lib()
+    need = lib.hexa_estmm_workspace_bytes(E, r.row_capacity, M, N, Lb.BF16)
+    assert need > 0, "this shape is meant to take the split path"
+    got = ops.estmm(ps, qs, r, out_dtype=out_dtype, engine=Lb.ENGINE_TCGEN05, ranks=ranks)
+    flat = got.permute(1, 0, 2, 3).reshape(E, M, N) if ranks > 1 else got
+    want = O.estmm(p, q, ids[:, 0], E)
+    tol = 2e-5 if out_dtype == torch.float32 else 2e-2
+    assert rel_err(flat, want) < tol, rel_err(flat, want)
+    if E > 1:
+        assert (flat[E - 1] == 0).all()
+    for _ in range(3):
+        assert torch.equal(ops.estmm(ps, qs, r, out_dtype=out_dtype, engine=Lb.ENGINE_TCGEN05, ranks=ranks), got)
+    # the unsplit kernel (no scratch offered) on the same inputs
+    plain = torch.empty(E, M, N, dtype=out_dtype, device="cuda")
+    Lb.check(lib.hexa_estmm(ps.data_ptr(), ps.stride(0), qs.data_ptr(), qs.stride(0), r.pad_offsets.data_ptr(), E, r.row_capacity,
+                            M, N, plain.data_ptr(), plain.stride(1), plain.stride(0), 0, 0, Lb.BF16, Lb.dt(plain), 0,
+                            Lb.ENGINE_TCGEN05, None, 0, torch.cuda.current_stream().cuda_stream), "hexa_estmm")
+    assert rel_err(flat, plain) < (2e-6 if out_dtype == torch.float32 else 1e-2)
+    if ranks == 1:
+        twice = ops.estmm(ps, qs, r, out=got.clone(), beta=1, engine=Lb.ENGINE_TCGEN05)
+        assert rel_err(twice, 2 * want) < max(tol, 1e-2 if out_dtype != torch.float32 else tol)
+
+
 @pytest.mark.parametrize("dtype,E,k,d,H,act", [(torch.float32, 8, 1, 128, 512, "gelu"), (torch.bfloat16, 8, 2, 256, 1024, "gelu"),
                                                (torch.float16, 5, 2, 128, 320, "relu"), (torch.bfloat16, 4, 2, 128, 256, "generic"),
                                                (torch.bfloat16, 4, 2, 128, 203, "gelu"), (torch.bfloat16, 3, 1, 256, 1639, "gelu"),
