@@ -37,7 +37,7 @@ from . import losses
 from .activations import classify
 from .gating import GATES, fused_topk_gshard
 from .layers import FusedMoE_Shared_CudaCore, MLP_Implement, simplified_extract_critical
-from .param_cache import PipelineSharedCache
+from .param_cache import DenseGradReducer, PipelineSharedCache
 
 
 class AttrDict(dict):
@@ -192,6 +192,7 @@ class MoE_Cascaded(torch.nn.Module):
         cfg.num_global_experts = int(num_global_experts)
         cfg.data_centric = bool(data_centric)
         cfg.cache = PipelineSharedCache(self) if data_centric else None
+        cfg.dense_reducer = DenseGradReducer(self.group) if self.world_size > 1 else None
         self.dispatch_params = cfg
 
         self._init_moe()

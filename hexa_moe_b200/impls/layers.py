@@ -188,6 +188,7 @@ class MLP_Implement(torch.autograd.Function):
     def forward(ctx: Any, config: Any, tokens_input: Tensor, fc1_w, fc2_w, fc1_bias, fc2_bias):
         ctx.config = config
         assert tokens_input.shape[1] == fc1_w.shape[1] and fc1_w.shape[0] == fc2_w.shape[0]
+        ctx.params = (fc1_w, fc2_w, fc1_bias, fc2_bias)
         dtype = tokens_input.dtype
         ctx.has_b1, ctx.has_b2 = fc1_bias is not None, fc2_bias is not None
         ctx.fused = _dense_on_kernels(config, tokens_input) and fc1_w.shape[0] % 8 == 0 and fc2_w.shape[1] % 8 == 0
@@ -237,6 +238,11 @@ class MLP_Implement(torch.autograd.Function):
             dx = d_hid @ fc1_w.to(dtype)
             dw1 = (d_hid.t() @ x).to(fc1_w.dtype)
             db1 = d_hid.sum(0).to(fc1_w.dtype) if ctx.has_b1 else None
+        reducer = getattr(cfg, "dense_reducer", None)
+        if _world(cfg.group) > 1 and reducer is not None and os.environ.get("HEXA_DEFER_GRADS", "1") != "0":
+            # bucketed, on a side stream, delivered to .grad when the backward pass ends (see DenseGradReducer)
+            reducer.add(list(zip(ctx.params, (dw1, dw2, db1, db2))))
+            return None, dx, None, None, None, None
         for g in (dw2, db2, dw1, db1):
             if g is not None:
                 all_reduce_avg(g, cfg.group)

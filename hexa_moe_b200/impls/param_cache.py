@@ -102,6 +102,85 @@ class BarrierWatchdog:
         self._thread = None
 
 
+class DenseGradReducer:
+    """Mean over the data-parallel ranks of the dense FFN layers' parameter gradients, bucketed and off the compute
+    stream.
+
+    The reference starts four asynchronous all-reduces per dense layer and waits for them before the layer's
+    backward returns (hexa_moe/impls/layers.py:62-88).  Here backward only copies the layer's gradients into a flat
+    bucket per dtype; a full bucket (HEXA_DENSE_BUCKET_MB, default 16) is all-reduced on a side stream while the rest
+    of the backward pass computes, and an autograd-engine callback at the end of the pass launches what is left,
+    waits, and hands every parameter a view of the reduced bucket as (or added to) its .grad.  One collective per
+    bucket instead of four per layer: a network like Swin-MoE-B has 14 dense layers of 2-8 MB of gradients each."""
+
+    def __init__(self, group):
+        self.group = group
+        self.side: Optional[torch.cuda.Stream] = None
+        self.bucket_bytes = int(float(os.environ.get("HEXA_DENSE_BUCKET_MB", "16")) * (1 << 20))
+        self._open = {}          # dtype -> [flat buffer, elements filled, [(param, offset, numel)]]
+        self._done = []          # (event | None, flat buffer, entries) of buckets already launched
+        self._queued = False
+
+    def add(self, pairs):
+        """pairs: [(parameter, gradient)] of one layer (gradients on the current stream)."""
+        for prm, g in pairs:
+            if g is None:
+                continue
+            st = self._open.get(g.dtype)
+            n = g.numel()
+            if st is not None and st[1] + n > st[0].numel():
+                self._launch(g.dtype)
+                st = None
+            if st is None:
+                cap = max(self.bucket_bytes // g.element_size(), n)
+                st = self._open[g.dtype] = [torch.empty(cap, dtype=g.dtype, device=g.device), 0, []]
+            st[0][st[1]: st[1] + n].copy_(g.reshape(-1))
+            st[2].append((prm, st[1], n))
+            st[1] += n
+            if st[1] >= st[0].numel():
+                self._launch(g.dtype)
+        if not self._queued:
+            self._queued = True
+            torch.autograd.Variable._execution_engine.queue_callback(self._flush)
+
+    def _launch(self, dtype):
+        flat, fill, entries = self._open.pop(dtype)
+        if fill == 0:
+            return
+        used = flat[:fill]
+        if used.is_cuda:
+            if self.side is None:
+                self.side = torch.cuda.Stream(device=used.device)
+            self.side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.side):
+                _layers.all_reduce_avg(used, self.group)
+                ev = torch.cuda.Event()
+                ev.record(self.side)
+        else:
+            _layers.all_reduce_avg(used, self.group)
+            ev = None
+        self._done.append((ev, flat, entries))
+
+    def _flush(self):
+        self._queued = False
+        try:
+            for dtype in list(self._open):
+                self._launch(dtype)
+            done, self._done = self._done, []
+            for ev, flat, entries in done:
+                if ev is not None:
+                    torch.cuda.current_stream().wait_event(ev)
+                    flat.record_stream(torch.cuda.current_stream())
+                for prm, off, n in entries:
+                    g = flat[off: off + n].view(prm.shape)
+                    if prm.grad is None:
+                        prm.grad = g
+                    else:
+                        prm.grad.add_(g)
+        finally:
+            self._open, self._done = {}, []
+
+
 class PipelineSharedCache:
     def __init__(self, owner):
         self.o = owner            # the MoE_Cascaded module (parameters, split tables, group)

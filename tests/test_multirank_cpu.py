@@ -206,3 +206,71 @@ def test_checkpoint_scatter_and_gather_two_ranks(proportion):
         p.join(60)
     for rank, msg in res:
         assert msg == "ok", f"rank {rank}: {msg}"
+
+
+def _dense_worker(rank, world, port, defer, q):
+    sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), HEXA_DEFER_GRADS=defer, HEXA_DENSE_BUCKET_MB="0.001")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle_backend
+        from hexa_moe import moe as hmoe
+        d, H = 16, 64
+        torch.manual_seed(5)                 # same parameters on both ranks
+        m = hmoe.MoE_Cascaded(gate_type={'type': 'top', 'k': 1}, model_dim_list=[d] * 3, moe_idx_list=[2], mlp_ratio=H // d,
+                              num_global_experts=2, total_depth=3, data_centric=True, activation_fn=lambda t: F.gelu(t))
+        m.dispatch_params.backend = oracle_backend
+        with torch.no_grad():
+            for n_, p in m.named_parameters():
+                if n_.startswith("mlp_"):
+                    p.normal_(0, 0.3)
+        x = torch.randn(24, d, generator=torch.Generator().manual_seed(50 + rank))
+        h = x
+        for depth in range(2):               # the two dense depths
+            h, aux = m(depth, h)
+            assert aux == 0
+        h.pow(2).sum().backward()
+        # expectation: plain autograd of the same FFNs, averaged over the ranks
+        names = ["mlp_fc1_w", "mlp_fc2_w", "mlp_fc1_b", "mlp_fc2_b"]
+        ref = [[getattr(m, n_)[i].detach().clone().requires_grad_(True) for n_ in names] for i in range(2)]
+        t = x
+        for w1, w2, b1, b2 in ref:
+            t = F.gelu(t @ w1.t() + b1) @ w2 + b2
+        t.pow(2).sum().backward()
+        for i in range(2):
+            for n_, r_ in zip(names, ref[i]):
+                want = r_.grad.clone()
+                dist.all_reduce(want)
+                want /= world
+                got = getattr(m, n_)[i].grad
+                assert got is not None and got.shape == want.shape, (n_, i)
+                torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
+        q.put((rank, "ok"))
+    except Exception:  # noqa: BLE001
+        import traceback
+        q.put((rank, "FAIL: " + traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("defer", ["1", "0"])
+def test_dense_ffn_gradients_are_averaged_over_ranks(defer):
+    """Dense depths (reference impls/layers.py:18-88): parameter gradients are the mean over the data-parallel ranks,
+    whether they travel in buckets on a side path and land in .grad at the end of backward (default; the tiny bucket
+    size here forces several buckets) or are all-reduced inline and returned through autograd (HEXA_DEFER_GRADS=0)."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_dense_worker, args=(r, world, port, defer, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        res = [q.get(timeout=240) for _ in range(world)]
+    finally:
+        for p in procs:
+            p.join(60)
+            if p.is_alive():
+                p.kill()
+    for rank, msg in res:
+        assert msg == "ok", f"rank {rank}: {msg}"
