@@ -109,6 +109,7 @@ _status_words = {}
 def ensure_status_word(device_index: int):
     w = _status_words.get(device_index)
     if w is None:
+        lib()                      # loaded before the lock is taken: lib() takes the same (non-reentrant) lock
         with _lock:
             w = _status_words.get(device_index)
             if w is None:

@@ -16,9 +16,11 @@
 //   warp 1      MMA issuer (only in the pair's leader CTA when CTAS = 2): one thread issues tcgen05.mma
 //               (K = 16 per instruction) into one of two TMEM accumulators; tcgen05.commit frees ring slots
 //               and publishes finished accumulators (multicast to both CTAs of a pair)
-//   warps 2..   epilogue (16 warps): tcgen05.ld of the accumulator (lane quadrant = warp % 4, each group of
-//               four warps owns a column range), fused epilogue math; ESMM results go through a 64B-swizzled
-//               staging tile and one TMA store per 128x32 block, ESTMM stores from registers
+//   warps 2..   epilogue (EW = 16 or 8 warps, template parameter): tcgen05.ld of the accumulator (lane quadrant =
+//               warp % 4, each group of four warps owns a column range), fused epilogue math; ESMM results go through
+//               a 64B-swizzled staging tile and one TMA store per 128x32 block, ESTMM stores from registers.  The
+//               MMA and producer threads share their issue slots with the epilogue warps of their sub-partition:
+//               16 warps finish a tile's epilogue sooner (short k-loops), 8 leave the role threads more slots
 // so the epilogue of tile i overlaps the MMAs of tile i+1.  Every mbarrier wait is bounded: after ~2 s a CTA
 // raises an abort flag, records a code in the status word and drains; both CTAs of a pair always reach the
 // closing cluster barrier.
@@ -40,8 +42,6 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;   // one 128-byte swizzle span of 16-bit elements
 constexpr int UMMA_K = 16;
-constexpr int kEpiWarps = 16;
-constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr uint32_t kABytes = BLOCK_M * BLOCK_K * 2;  // 16 KB
 
 enum Mode { ESMM_NK = 0, ESMM_KN = 1, ESTMM = 2 };
@@ -298,14 +298,18 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                : "memory");
 }
 
-template <int BN, int CTAS> struct Cfg {
-  static constexpr int kStages = (BN == 256 && CTAS == 1) ? 4 : 6;
+template <int BN, int CTAS, int EW, int MODE> struct Cfg {
+  static constexpr int kThreads = 32 * (2 + EW);
+  // ESTMM stores from registers and needs no staging tile: its ring gets the space (one more 32 KB slot), which is what
+  // a loop bounded by the latency of a ring slot's round trip (MMA done -> slot refilled) converts into throughput
+  static constexpr int kStages = (BN == 256 && CTAS == 1) ? 4 : (MODE == ESTMM ? 7 : 6);
   static constexpr uint32_t kBBytes = (BN / CTAS) * BLOCK_K * 2;   // this CTA's share of the B tile
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators; 256 or 512, a power of two
   static constexpr uint32_t kStoreBufBytes = 128 * 64;   // [128 rows x 32 16-bit columns]
-  static constexpr uint32_t kStoreBytes = 4 * kStoreBufBytes;  // one buffer per group of four epilogue warps
+  static constexpr uint32_t kStoreBytes = MODE == ESTMM ? 0 : (EW / 4) * kStoreBufBytes;  // one buffer per group of four epilogue warps
   static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + kStoreBytes + 256 /*barriers*/;
+  static_assert(kSmemBytes <= 232448, "more shared memory than one CTA can have (227 KB)");
 };
 
 struct Tile {
@@ -422,11 +426,12 @@ __device__ __forceinline__ void epi_values16(const float (&f)[16], const uint16_
   }
 }
 
-template <int BN, int MODE, int CTAS>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, int MODE, int CTAS, int EW>
+__global__ void __launch_bounds__(32 * (2 + EW), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const Params p) {
-  using C = Cfg<BN, CTAS>;
+  using C = Cfg<BN, CTAS, EW, MODE>;
+  constexpr int kEpiWarps = EW;
   constexpr int kStages = C::kStages;
   constexpr int BNH = BN / CTAS;          // B columns this CTA loads
   extern __shared__ uint8_t smem_raw[];
@@ -439,7 +444,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* acc_empty = bars + 2 * kStages + 2;   // [2] epilogues -> MMA    (used in the leader CTA)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* group_abort = abort_flag + 1;   // [kEpiWarps / 4]: one per group of four epilogue warps
+  volatile int* group_abort = abort_flag + 1;   // [4]: one per group of four epilogue warps
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = CTAS == 2 ? (int)cluster_ctarank() : 0;    // 0 = leader of the pair
@@ -831,13 +836,13 @@ int make_map(CUtensorMap* tm, const void* base, int is_bf16, int rank, const uin
   return HEXA_OK;
 }
 
-template <int BN, int MODE, int CTAS>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX, const Params& p,
-           int64_t max_tiles, cudaStream_t stream) {
-  using C = Cfg<BN, CTAS>;
+template <int BN, int MODE, int CTAS, int EW>
+int launch_ew(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX, const Params& p,
+              int64_t max_tiles, cudaStream_t stream) {
+  using C = Cfg<BN, CTAS, EW, MODE>;
   static bool attr_set[64] = {false};
   static int max_clusters[64] = {0};
-  auto kernel = gemm_tc_kernel<BN, MODE, CTAS>;
+  auto kernel = gemm_tc_kernel<BN, MODE, CTAS, EW>;
   int dev = 0;
   HEXA_CUDA(cudaGetDevice(&dev));
   HEXA_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
@@ -847,7 +852,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   }
   if (max_tiles <= 0) return HEXA_OK;
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(C::kThreads);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -871,7 +876,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   }
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, tmX, p);
   if (e != cudaSuccess) {
-    set_error("launch of gemm_tc_kernel<%d,%d,%d> failed: %s", BN, MODE, CTAS, cudaGetErrorString(e));
+    set_error("launch of gemm_tc_kernel<%d,%d,%d,%d> failed: %s", BN, MODE, CTAS, EW, cudaGetErrorString(e));
     return HEXA_ERR_CUDA;
   }
   return HEXA_OK;
@@ -880,6 +885,23 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
 int env_int(const char* name, int dflt) {
   const char* s = getenv(name);
   return s ? atoi(s) : dflt;
+}
+
+// Epilogue warps of a launch: HEXA_TC_EPI_WARPS (8 or 16, read at every launch so that one process can compare the two)
+// or, by default, 8 for long k-loops and 16 for short ones, where the epilogue of a tile has to keep pace with few MMAs.
+int epi_warps_for(int64_t num_kb_typical) {
+  const int forced = env_int("HEXA_TC_EPI_WARPS", 0);
+  if (forced == 4 || forced == 8 || forced == 16) return forced;
+  const int64_t threshold = env_int("HEXA_TC_EPI_WARPS_KB", 0);     // 0: always 16 (the measured default, see DESIGN)
+  return (threshold > 0 && num_kb_typical >= threshold) ? 8 : 16;
+}
+
+template <int BN, int MODE, int CTAS>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmX, const Params& p,
+           int64_t max_tiles, cudaStream_t stream, int epi_warps) {
+  if (epi_warps == 4) return launch_ew<BN, MODE, CTAS, 4>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
+  if (epi_warps == 8) return launch_ew<BN, MODE, CTAS, 8>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
+  return launch_ew<BN, MODE, CTAS, 16>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
 }
 // HEXA_TC_CTAS=1 keeps every GEMM on single-CTA tiles (for A/B measurements); default: CTA pairs where they apply.
 bool pairs_enabled() { static int v = -1; if (v < 0) v = env_int("HEXA_TC_CTAS", 2) == 1 ? 0 : 1; return v == 1; }
@@ -952,17 +974,18 @@ int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int6
   p.n = n_out; p.k = k; p.m = 0; p.E = E; p.epilogue = epilogue; p.act = act; p.is_bf16 = is_bf16;
   p.status = status_word(); p.debug = tc_debug_flags(); p.wait_limit_ns = wait_limit_ns();
   const int64_t NT = ceil_div(n_out, BN);
+  const int ew = epi_warps_for(ceil_div(k, BLOCK_K));
   if (ctas == 2) {
     const int64_t max_tiles = p.max_pairs * NT;
-    return b_layout == HEXA_B_NK ? launch<256, ESMM_NK, 2>(tmA, tmB, tmC, tmX, p, max_tiles, stream)
-                                 : launch<256, ESMM_KN, 2>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
+    return b_layout == HEXA_B_NK ? launch<256, ESMM_NK, 2>(tmA, tmB, tmC, tmX, p, max_tiles, stream, ew)
+                                 : launch<256, ESMM_KN, 2>(tmA, tmB, tmC, tmX, p, max_tiles, stream, ew);
   }
   const int64_t max_tiles = (row_cap / BLOCK_M) * NT;
   if (b_layout == HEXA_B_NK)
-    return BN == 256 ? launch<256, ESMM_NK, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream)
-                     : launch<128, ESMM_NK, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
-  return BN == 256 ? launch<256, ESMM_KN, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream)
-                   : launch<128, ESMM_KN, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream);
+    return BN == 256 ? launch<256, ESMM_NK, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream, ew)
+                     : launch<128, ESMM_NK, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream, ew);
+  return BN == 256 ? launch<256, ESMM_KN, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream, ew)
+                   : launch<128, ESMM_KN, 1>(tmA, tmB, tmC, tmX, p, max_tiles, stream, ew);
 }
 
 bool estmm_tc_supported(const void* p, int64_t ldp, const void* q, int64_t ldq, const void* out, int64_t ldo,
@@ -1039,9 +1062,10 @@ int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, con
   const int64_t max_tiles = (int64_t)E * ceil_div(m, BLOCK_M * ctas) * ceil_div(n, BN) * splits;
   // ESTMM stores straight from registers; the two output maps are unused placeholders
   int rc;
-  if (ctas == 2) rc = launch<256, ESTMM, 2>(tmA, tmB, tmA, tmA, p, max_tiles, stream);
-  else rc = BN == 256 ? launch<256, ESTMM, 1>(tmA, tmB, tmA, tmA, p, max_tiles, stream)
-                      : launch<128, ESTMM, 1>(tmA, tmB, tmA, tmA, p, max_tiles, stream);
+  const int ew = epi_warps_for(row_cap / BLOCK_K / (E * (int64_t)splits));
+  if (ctas == 2) rc = launch<256, ESTMM, 2>(tmA, tmB, tmA, tmA, p, max_tiles, stream, ew);
+  else rc = BN == 256 ? launch<256, ESTMM, 1>(tmA, tmB, tmA, tmA, p, max_tiles, stream, ew)
+                      : launch<128, ESTMM, 1>(tmA, tmB, tmA, tmA, p, max_tiles, stream, ew);
   if (rc != HEXA_OK || splits == 1) return rc;
   const int64_t total = (int64_t)E * m * (n / 4);
   int64_t blocks = ceil_div(total, 256);

@@ -216,3 +216,30 @@ def test_barrier_watchdog_thread_trips_on_a_real_clock():
         time.sleep(0.02)
     assert hit == [1] and "left between steps" in wd.failed and time.monotonic() - t0 < 5.0
     wd.stop()
+
+
+def test_installing_the_status_word_in_a_fresh_process_does_not_deadlock():
+    """The first operator call of a process installs the device status word; that path loads the library under the
+    same lock it is about to take.  Run in a fresh interpreter (the library not loaded yet) with the two CUDA-only
+    steps replaced: the call must get as far as the C entry point (which, without a device, answers with an error)."""
+    import subprocess
+    import sys
+    code = r'''
+import sys, threading, contextlib
+sys.path.insert(0, %r)
+import torch
+from hexa_moe_b200 import _lib as L
+torch.Tensor.pin_memory = lambda self: self
+torch.cuda.device = lambda idx: contextlib.nullcontext()
+out = []
+def run():
+    try:
+        L.ensure_status_word(0)
+        out.append("installed")
+    except L.HexaError as e:
+        out.append("entry point reached: " + str(e)[:60])
+t = threading.Thread(target=run, daemon=True); t.start(); t.join(60)
+print("DEADLOCK" if t.is_alive() else out[0])
+''' % ROOT
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=180)
+    assert "DEADLOCK" not in res.stdout and ("installed" in res.stdout or "entry point reached" in res.stdout), res.stdout + res.stderr
