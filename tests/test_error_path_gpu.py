@@ -69,7 +69,8 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_keeps_working(ops, n_ou
     L.clear_device_status()
     again = ops.esmm(xs, w, L.B_NK, r, engine=L.ENGINE_TCGEN05)     # same context, same answer as before
     torch.cuda.synchronize()
-    assert torch.equal(again, good) and L.device_status() == 0
+    n_pad = int(r.pad_offsets[-1])                                  # rows beyond the last segment are never written
+    assert torch.equal(again[:n_pad], good[:n_pad]) and L.device_status() == 0
 
 
 def test_status_word_is_shared_by_host_threads(ops):

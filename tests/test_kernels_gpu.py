@@ -319,7 +319,7 @@ def test_estmm_split_segments(ops, E, M, N, out_dtype, ranks):
     Lb.check(lib.hexa_estmm(ps.data_ptr(), ps.stride(0), qs.data_ptr(), qs.stride(0), r.pad_offsets.data_ptr(), E, r.row_capacity,
                             M, N, plain.data_ptr(), plain.stride(1), plain.stride(0), 0, 0, Lb.BF16, Lb.dt(plain), 0,
                             Lb.ENGINE_TCGEN05, None, 0, torch.cuda.current_stream().cuda_stream), "hexa_estmm")
-    assert rel_err(flat, plain) < (2e-6 if out_dtype == torch.float32 else 1e-2)
+    assert rel_err(flat, plain) < (2e-5 if out_dtype == torch.float32 else 1e-2)     # fp32: another summation order
     if ranks == 1:
         twice = ops.estmm(ps, qs, r, out=got.clone(), beta=1, engine=Lb.ENGINE_TCGEN05)
         assert rel_err(twice, 2 * want) < max(tol, 1e-2 if out_dtype != torch.float32 else tol)
