@@ -11,21 +11,60 @@
 namespace hexa {
 namespace {
 
-template <typename T>
-__global__ void mean_slices_kernel(const T* __restrict__ local, const T* __restrict__ recv, int n_recv, int64_t elems,
-                                   float scale, T* __restrict__ out) {
+// The kernel runs on a side stream next to the persistent GEMM kernels, which leave room for one small block per SM
+// (about 10K registers and no shared memory), so its bandwidth comes from loads in flight per thread, not from
+// occupancy: a thread fetches the same 16-byte vector of all S slices for U positions at once (S * U = 8 independent
+// loads) before it adds anything.  S = n_recv + 1 when that is 2, 4 or 8; other counts take the generic loop.
+template <typename T, int S, int U>
+__global__ void __launch_bounds__(128)
+mean_slices_kernel(const T* __restrict__ local, const T* __restrict__ recv, int n_recv, int64_t elems, float scale,
+                   T* __restrict__ out) {
   constexpr int V = 16 / sizeof(T);
   const int64_t nvec = elems / V;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const uint4* loc4 = reinterpret_cast<const uint4*>(local);
+  const uint4* rcv4 = reinterpret_cast<const uint4*>(recv);
+  uint4* out4 = reinterpret_cast<uint4*>(out);
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (S > 0) {
+    for (; i + (U - 1) * stride < nvec; i += U * stride) {
+      uint4 raw[U][S > 0 ? S : 1];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        raw[u][0] = __ldg(loc4 + i + u * stride);
+#pragma unroll
+        for (int s = 1; s < S; ++s) raw[u][s] = __ldg(rcv4 + (int64_t)(s - 1) * nvec + i + u * stride);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float acc[V];
+        const T* v0 = reinterpret_cast<const T*>(&raw[u][0]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] = to_f32<T>(v0[j]);
+#pragma unroll
+        for (int s = 1; s < S; ++s) {           // fixed order: local, then the received slices by index
+          const T* v = reinterpret_cast<const T*>(&raw[u][s]);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] += to_f32<T>(v[j]);
+        }
+        uint4 o;
+        T* ov = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int j = 0; j < V; ++j) ov[j] = from_f32<T>(acc[j] * scale);
+        out4[i + u * stride] = o;
+      }
+    }
+  }
+  for (; i < nvec; i += stride) {      // generic slice count, and the tail of the unrolled loop
     float acc[V];
     {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(local) + i);
+      const uint4 raw = __ldg(loc4 + i);
       const T* v = reinterpret_cast<const T*>(&raw);
 #pragma unroll
       for (int j = 0; j < V; ++j) acc[j] = to_f32<T>(v[j]);
     }
     for (int s = 0; s < n_recv; ++s) {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(recv + (int64_t)s * elems) + i);
+      const uint4 raw = __ldg(rcv4 + (int64_t)s * nvec + i);
       const T* v = reinterpret_cast<const T*>(&raw);
 #pragma unroll
       for (int j = 0; j < V; ++j) acc[j] += to_f32<T>(v[j]);
@@ -34,7 +73,21 @@ __global__ void mean_slices_kernel(const T* __restrict__ local, const T* __restr
     T* ov = reinterpret_cast<T*>(&o);
 #pragma unroll
     for (int j = 0; j < V; ++j) ov[j] = from_f32<T>(acc[j] * scale);
-    reinterpret_cast<uint4*>(out)[i] = o;
+    out4[i] = o;
+  }
+}
+
+template <typename T>
+void mean_slices_launch(const void* local, const void* recv, int n_recv, int64_t elems, float scale, void* out, unsigned blocks,
+                        cudaStream_t stream) {
+  const T* l = static_cast<const T*>(local);
+  const T* r = static_cast<const T*>(recv);
+  T* o = static_cast<T*>(out);
+  switch (n_recv + 1) {
+    case 2: mean_slices_kernel<T, 2, 4><<<blocks, 128, 0, stream>>>(l, r, n_recv, elems, scale, o); break;
+    case 4: mean_slices_kernel<T, 4, 2><<<blocks, 128, 0, stream>>>(l, r, n_recv, elems, scale, o); break;
+    case 8: mean_slices_kernel<T, 8, 1><<<blocks, 128, 0, stream>>>(l, r, n_recv, elems, scale, o); break;
+    default: mean_slices_kernel<T, 0, 1><<<blocks, 128, 0, stream>>>(l, r, n_recv, elems, scale, o); break;
   }
 }
 
@@ -74,13 +127,14 @@ extern "C" int hexa_mean_slices(const void* local, const void* recv, int n_recv,
   HEXA_REQUIRE(elems % V == 0, "hexa_mean_slices: element count must be a multiple of %d", V);
   if (elems == 0) return HEXA_OK;
   const float scale = 1.0f / (float)world;
-  int64_t blocks = ceil_div(elems / V, 256);
-  const int64_t cap = (int64_t)sm_count() * 8;
+  int64_t blocks = ceil_div(elems / V, 128 * 8);
+  const int64_t cap = (int64_t)sm_count() * 2;      // at most two waves of one-block-per-SM residency
   if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
   switch (dtype) {
-    case HEXA_F32: mean_slices_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>((const float*)local, (const float*)recv, n_recv, elems, scale, (float*)out); break;
-    case HEXA_F16: mean_slices_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>((const __half*)local, (const __half*)recv, n_recv, elems, scale, (__half*)out); break;
-    case HEXA_BF16: mean_slices_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)local, (const __nv_bfloat16*)recv, n_recv, elems, scale, (__nv_bfloat16*)out); break;
+    case HEXA_F32: mean_slices_launch<float>(local, recv, n_recv, elems, scale, out, (unsigned)blocks, stream); break;
+    case HEXA_F16: mean_slices_launch<__half>(local, recv, n_recv, elems, scale, out, (unsigned)blocks, stream); break;
+    case HEXA_BF16: mean_slices_launch<__nv_bfloat16>(local, recv, n_recv, elems, scale, out, (unsigned)blocks, stream); break;
     default: HEXA_REQUIRE(false, "hexa_mean_slices: bad dtype %d", dtype);
   }
   HEXA_LAUNCH_CHECK("mean_slices");

@@ -270,7 +270,7 @@ extern "C" int hexa_set_wait_limit_ns(uint64_t ns) {
   return HEXA_OK;
 }
 extern "C" int hexa_set_tc_debug(int flags) {
-  HEXA_REQUIRE(flags >= 0 && flags < 8, "hexa_set_tc_debug: flags must be a combination of bits 0..2");
+  HEXA_REQUIRE(flags >= 0 && flags < 64, "hexa_set_tc_debug: flags must be a combination of bits 0..5");
   hexa::g_tc_debug = flags;
   return HEXA_OK;
 }

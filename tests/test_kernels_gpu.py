@@ -354,6 +354,25 @@ def test_layer_forward_backward(ops, dtype, E, k, d, H, act):
         assert e < tol, (name, e)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("n_recv", [0, 1, 2, 3, 5, 7])
+def test_mean_slices(ops, dtype, n_recv):
+    """The reduction step of the peer-copy reduce-scatter: out = (local + received slices) / world with fp32
+    accumulation in slice order, for slice counts with and without an unrolled variant and sizes that leave a tail."""
+    world = n_recv + 1
+    for elems in (8 * 1000, 8 * 128 * 8 * 37 + 8 * 5, 1 << 22):
+        g = torch.Generator().manual_seed(elems % 1000 + n_recv)
+        local = torch.randn(elems, generator=g).to(dtype).cuda()
+        recv = torch.randn(max(n_recv, 1), elems, generator=g).to(dtype).cuda()
+        out = torch.empty_like(local)
+        ops.mean_slices(local, recv, n_recv, world, out)
+        acc = local.float()
+        for s_ in range(n_recv):
+            acc = acc + recv[s_].float()
+        want = (acc * (1.0 / world)).to(dtype)
+        assert torch.equal(out, want), (elems, float((out.float() - want.float()).abs().max()))
+
+
 def test_errors_are_reported_not_fatal(ops):
     Lb = L()
     ids = make_ids(64, 1, 4, 0)
