@@ -68,7 +68,10 @@ def parse():
     return ap.parse_args()
 
 
-TRAFFIC_RATIO = 1.0      # dram bytes per launch / algorithmic bytes per launch of the GEMM kernels, from the ncu capture
+# dram bytes per launch / algorithmic bytes per launch of the GEMM kernels by launch type, from an ncu capture of one
+# launch of each type at the headline d / hidden with 8 experts (same rows per expert, so traffic scales with the experts)
+TRAFFIC_RATIO = {"esmm:fc1_forward_act": 1.27, "esmm:fc2_forward": 1.92, "estmm:dw2": 1.29, "esmm:fc2_dgrad_dact": 1.36,
+                 "estmm:dw1": 1.29, "esmm:fc1_dgrad": 1.92}
 
 
 def peaks():
@@ -688,7 +691,8 @@ def main():
     # DRAM bytes per launch: ncu captures of these kernels (dram read + write per launch against the algorithmic
     # operand + output bytes, one launch of each type) give the ratio; the headline workload itself is too large to
     # capture, so `traffic` is the algorithmic bytes of the timed launches times that measured ratio
-    ratio = TRAFFIC_RATIO
+    traffic_bytes = sum(v[3] * TRAFFIC_RATIO.get(n_, 1.5) for n_, v in per_type.items())
+    ratio = traffic_bytes / gemm_by if gemm_by > 0 else 1.0
     by_type = {n_: dict(launches=v[0], avg_ms=round(v[1] / v[0], 4), tflops=round(v[2] / (v[1] * 1e-3) / 1e12, 1),
                         frac_of_sustained=round(v[2] / (v[1] * 1e-3) / 1e12 / pk["tflops"], 3),
                         frac_of_burst=round(v[2] / (v[1] * 1e-3) / 1e12 / pk["burst"], 3))
@@ -697,9 +701,9 @@ def main():
                     unit="TFLOP/s", frac=achieved / pk["tflops"], peak_source=pk["source"] + " (sustained cuBLAS bf16)",
                     frac_of_burst=achieved / pk["burst"], burst_peak=pk["burst"],
                     launches=gemm_n, avg_launch_ms=gemm_ms / max(gemm_n, 1), flops_per_launch=gemm_fl / max(gemm_n, 1),
-                    traffic=ratio * gemm_by / max(gemm_n, 1),
-                    traffic_source="algorithmic bytes x %.2f (dram bytes / algorithmic bytes of an ncu capture at the "
-                                   "headline d / hidden with 8 experts)" % ratio,
+                    traffic=traffic_bytes / max(gemm_n, 1), algorithmic_bytes=gemm_by / max(gemm_n, 1),
+                    traffic_source="algorithmic bytes of the timed launches x the dram/algorithmic ratio of their launch "
+                                   "type (%.2f on average) measured by ncu at the headline d / hidden with 8 experts" % ratio,
                     by_launch_type=by_type)
     kernels = {n_: dict(calls=v[0], ms_total=round(v[1], 3)) for n_, v in per.items()}
     my_kernel_ms = sum(v[1] for v in per.values()) / args.steps

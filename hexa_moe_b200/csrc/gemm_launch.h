@@ -7,14 +7,14 @@
 namespace hexa {
 int esmm_simt_launch(const void*, int64_t, const void*, int, int64_t, int64_t, const float*, int64_t, void*, int64_t, void*,
                      int64_t, const int32_t*, const int32_t*, const int32_t*, int, int64_t, int64_t, int64_t, int, int, int,
-                     cudaStream_t);
+                     cudaStream_t, int e_begin, int e_end);
 int estmm_simt_launch(const void*, int64_t, const void*, int64_t, const int32_t*, int, int64_t, int64_t, void*, int64_t,
                       int64_t, int64_t, int64_t, int, int, int, cudaStream_t);
 bool esmm_tc_supported(const void*, int64_t, const void*, int64_t, int64_t, const void*, int64_t, const void*, int64_t,
                        const float*, int64_t, int64_t, int);
 int esmm_tc_launch(const void*, int64_t, const void*, int, int64_t, int64_t, const float*, int64_t, void*, int64_t, void*,
                    int64_t, const int32_t*, const int32_t*, const int32_t*, const int32_t*, int, int64_t, int64_t, int64_t, int,
-                   int, int, cudaStream_t);
+                   int, int, cudaStream_t, int e_begin, int e_end);
 bool estmm_tc_supported(const void*, int64_t, const void*, int64_t, const void*, int64_t, int64_t, int64_t, int64_t, int, int);
 int estmm_tc_launch(const void*, int64_t, const void*, int64_t, const int32_t*, int, int64_t, int64_t, int64_t, void*, int64_t,
                     int64_t, int64_t, int64_t, int, int, int, cudaStream_t, void* const* split_out = nullptr, int n_split = 0,

@@ -16,13 +16,13 @@ esmm_simt_kernel(const T* __restrict__ a, int64_t lda, const T* __restrict__ b, 
                  int64_t b_estride, const float* __restrict__ bias, int64_t ldbias, T* __restrict__ aux, int64_t ldaux,
                  T* __restrict__ c, int64_t ldc, const int32_t* __restrict__ tile_expert,
                  const int32_t* __restrict__ pad_offsets, const int32_t* __restrict__ row_token, int E, int64_t n_out,
-                 int64_t k, int epilogue, int act) {
+                 int64_t k, int epilogue, int act, int e_begin, int e_end) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
   const int64_t row0 = (int64_t)blockIdx.y * BM;
   if (row0 >= pad_offsets[E]) return;
   const int e = tile_expert[row0 / kRowTile];
-  if (e < 0) return;
+  if (e < e_begin || e >= e_end) return;      // also the -1 of tiles beyond the last segment
   const int64_t n0 = (int64_t)blockIdx.x * BN;
   const T* be = b + (int64_t)e * b_estride;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -159,14 +159,16 @@ estmm_simt_kernel(const T* __restrict__ p, int64_t ldp, const T* __restrict__ q,
 int esmm_simt_launch(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
                      const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
                      const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token, int E,
-                     int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue, int act, cudaStream_t stream) {
-  if (row_cap == 0) return HEXA_OK;
+                     int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue, int act, cudaStream_t stream,
+                     int e_begin, int e_end) {
+  if (row_cap == 0 || e_begin >= e_end) return HEXA_OK;
+  if (e_begin < 0) e_begin = 0;
   dim3 grid((unsigned)ceil_div(n_out, BN), (unsigned)(row_cap / BM));
   HEXA_REQUIRE(grid.y <= 65535, "hexa_esmm (simt): row_capacity %lld too large", (long long)row_cap);
 #define HEXA_ESMM_SIMT(T)                                                                                             \
   esmm_simt_kernel<T><<<grid, 256, 0, stream>>>((const T*)a, lda, (const T*)b, b_layout, ldb, b_estride, bias, ldbias, \
                                                 (T*)aux, ldaux, (T*)c, ldc, tile_expert, pad_offsets, row_token, E,   \
-                                                n_out, k, epilogue, act)
+                                                n_out, k, epilogue, act, e_begin, e_end)
   switch (dtype) {
     case HEXA_F32: HEXA_ESMM_SIMT(float); break;
     case HEXA_F16: HEXA_ESMM_SIMT(__half); break;

@@ -66,6 +66,7 @@ struct Params {
   int64_t k;        // ESMM: contraction length ; ESTMM: unused
   int64_t m;        // ESTMM: output rows per expert
   int E;
+  int e_begin, e_end;   // ESMM: only tiles of experts in [e_begin, e_end) are computed by this launch
   int epilogue, act;
   int is_bf16;      // 16-bit flavour of the inputs (and of 16-bit outputs)
   int out_f32;      // ESTMM: fp32 output
@@ -319,6 +320,7 @@ struct Tile {
   int m0;         // ESTMM: first output row of this CTA's block
   int num_kb;     // k-blocks to accumulate
   int valid;      // this CTA has rows to store (the second CTA of a pair may not)
+  int skip;       // ESMM: the tile's expert is outside the launch's expert range (every role skips it alike)
   int split;      // ESTMM with splits > 1: which chunk of the segment this tile covers
 };
 
@@ -342,6 +344,7 @@ __device__ __forceinline__ bool get_tile(const Params& p, int64_t t, int rank, T
     tile.row0 = seg0 + kb0 * BLOCK_K;
     tile.num_kb = max(0, min(kb_per, kb_all - kb0));
     tile.split = c;
+    tile.skip = 0;
     tile.valid = tile.m0 < p.m;
     return true;
   } else {
@@ -367,6 +370,7 @@ __device__ __forceinline__ bool get_tile(const Params& p, int64_t t, int rank, T
     tile.col0 = (int)(t % NT) * BN;
     tile.m0 = 0;
     tile.num_kb = (int)((p.k + BLOCK_K - 1) / BLOCK_K);
+    tile.skip = tile.e < p.e_begin || tile.e >= p.e_end;
     return tile.e >= 0;
   }
 }
@@ -481,6 +485,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       Tile tile;
       const uint32_t lead_full0 = CTAS == 2 ? map_to_cta(&full[0], 0) : 0u;   // the leader CTA's first full barrier
       for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step) {
+        if (MODE != ESTMM && tile.skip) continue;
         for (int kb = 0; kb < tile.num_kb; ++kb) {
           if (!(ok = mbar_wait_fast(&empty[stage], phase ^ 1, abort_flag, p.status, 1, p.wait_limit_ns))) break;
           uint8_t* sA = smem + (size_t)stage * C::kStageBytes;
@@ -557,8 +562,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       Tile tile;
-      int it = 0;
-      for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step, ++it) {
+      int it = -1;
+      for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step) {
+        if (MODE != ESTMM && tile.skip) continue;
+        ++it;
         const int acc = it & 1;
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
         if (!(ok = mbar_wait_fast(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, 2, p.wait_limit_ns))) break;
@@ -601,8 +608,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* buf = store_bufs + (size_t)part * C::kStoreBufBytes;
     bool ok = true;
     Tile tile;
-    int it = 0;
-    for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step, ++it) {
+    int it = -1;
+    for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step) {
+      if (MODE != ESTMM && tile.skip) continue;
+      ++it;
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
       // The four warps of a group meet at named barriers inside the tile, so they must leave together: each warp
@@ -711,7 +720,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (is_bf16) epi_values16<E_, A_, 1>(f, xp, live, ncols, yh, oh);                                  \
     else epi_values16<E_, A_, 0>(f, xp, live, ncols, yh, oh);                                          \
     break;
-            switch (p.epilogue * 8 + p.act) {
+            switch ((p.debug & 8) ? 99 : p.epilogue * 8 + p.act) {
               HEXA_EPI_CASE(HEXA_EPI_ACT, HEXA_ACT_RELU)
               HEXA_EPI_CASE(HEXA_EPI_ACT, HEXA_ACT_GELU)
               HEXA_EPI_CASE(HEXA_EPI_ACT, HEXA_ACT_GELU_TANH)
@@ -729,8 +738,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #undef HEXA_EPI_CASE
           }
           // registers -> swizzled staging tile -> one TMA store per 128x32 block (full 128-byte lines to L2)
-          const bool two = (p.epilogue == HEXA_EPI_ACT) && p.aux != nullptr;
-          for (int o = two ? 0 : 1; o < 2; ++o) {
+          const bool two = (p.epilogue == HEXA_EPI_ACT) && p.aux != nullptr && !(p.debug & 16);
+          for (int o = (p.debug & 32) ? 2 : (two ? 0 : 1); o < 2; ++o) {
             if (leader) bulk_wait_read<0>();   // the previous store has finished reading the buffer
             group_sync(1 + part);
             stage_row(buf, rloc, o == 0 ? yv : ov);
@@ -926,8 +935,8 @@ int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int6
                    const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
                    const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
                    const int32_t* pair_block, int E, int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue,
-                   int act, cudaStream_t stream) {
-  if (row_cap == 0) return HEXA_OK;
+                   int act, cudaStream_t stream, int e_begin, int e_end) {
+  if (row_cap == 0 || e_begin >= e_end) return HEXA_OK;
   const int is_bf16 = dtype == HEXA_BF16;
   const int BN = n_out > 128 ? 256 : 128;
   const int ctas = (BN == 256 && pair_block != nullptr && pairs_enabled()) ? 2 : 1;
@@ -971,7 +980,8 @@ int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int6
   p.tile_expert = tile_expert; p.pad_offsets = pad_offsets; p.row_token = row_token;
   p.pair_block = pair_block; p.max_pairs = row_cap / (2 * BLOCK_M) + E;
   p.bias = bias; p.ldbias = ldbias; p.aux = aux; p.ldaux = ldaux; p.c = c; p.ldc = ldc;
-  p.n = n_out; p.k = k; p.m = 0; p.E = E; p.epilogue = epilogue; p.act = act; p.is_bf16 = is_bf16;
+  p.n = n_out; p.k = k; p.m = 0; p.E = E; p.e_begin = e_begin; p.e_end = e_end;
+  p.epilogue = epilogue; p.act = act; p.is_bf16 = is_bf16;
   p.status = status_word(); p.debug = tc_debug_flags(); p.wait_limit_ns = wait_limit_ns();
   const int64_t NT = ceil_div(n_out, BN);
   const int ew = epi_warps_for(ceil_div(k, BLOCK_K));

@@ -46,13 +46,15 @@ int ensure_store_access(const void* ptr, int dev, const char* who) {
 }
 }  // namespace
 
-extern "C" int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
-                         const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
-                         const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
-                         const int32_t* pair_block, int E, int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue,
-                         int act, int engine, void* stream_) {
+extern "C" int hexa_esmm_experts(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
+                                 const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
+                                 const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
+                                 const int32_t* pair_block, int E, int64_t row_cap, int64_t n_out, int64_t k, int dtype,
+                                 int epilogue, int act, int engine, int expert_begin, int expert_end, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   HEXA_REQUIRE(a && b && c && tile_expert && pad_offsets, "hexa_esmm: null pointer");
+  HEXA_REQUIRE(expert_begin >= 0 && expert_begin <= expert_end && expert_end <= E,
+               "hexa_esmm: expert range [%d, %d) is not inside [0, %d)", expert_begin, expert_end, E);
   HEXA_REQUIRE(E > 0 && row_cap >= 0 && row_cap % kRowTile == 0 && n_out > 0 && k > 0,
                "hexa_esmm: bad sizes (row_capacity must be a multiple of %d)", kRowTile);
   HEXA_REQUIRE(lda >= k && ldc >= n_out && (!aux || ldaux >= n_out) && (!bias || ldbias >= n_out), "hexa_esmm: leading dimension too small");
@@ -71,9 +73,18 @@ extern "C" int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout
   }
   if (engine != HEXA_ENGINE_SIMT && tc_ok)
     return esmm_tc_launch(a, lda, b, b_layout, ldb, b_estride, bias, ldbias, aux, ldaux, c, ldc, tile_expert, pad_offsets,
-                          row_token, pair_block, E, row_cap, n_out, k, dtype, epilogue, act, stream);
+                          row_token, pair_block, E, row_cap, n_out, k, dtype, epilogue, act, stream, expert_begin, expert_end);
   return esmm_simt_launch(a, lda, b, b_layout, ldb, b_estride, bias, ldbias, aux, ldaux, c, ldc, tile_expert, pad_offsets,
-                          row_token, E, row_cap, n_out, k, dtype, epilogue, act, stream);
+                          row_token, E, row_cap, n_out, k, dtype, epilogue, act, stream, expert_begin, expert_end);
+}
+
+extern "C" int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
+                         const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
+                         const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
+                         const int32_t* pair_block, int E, int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue,
+                         int act, int engine, void* stream_) {
+  return hexa_esmm_experts(a, lda, b, b_layout, ldb, b_estride, bias, ldbias, aux, ldaux, c, ldc, tile_expert, pad_offsets,
+                           row_token, pair_block, E, row_cap, n_out, k, dtype, epilogue, act, engine, 0, E, stream_);
 }
 
 extern "C" size_t hexa_estmm_workspace_bytes(int E, int64_t row_cap, int64_t m, int64_t n, int dtype) {

@@ -275,13 +275,17 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
             if W > 1:
                 # full expert weights of this layer from the pipeline-shared cache; start fetching the next layer's
                 # fc1 can start as soon as its weights are in; fc2's may still be arriving
-                w1, w2, b1 = cfg.cache.get(stage, wait=("w1", "b1"))
+                w1, w2, b1 = cfg.cache.get(stage, wait=("b1",))
                 cfg.cache.prefetch(stage + 1)                     # overlaps this layer's kernels
                 cfg.cache.limit_compute_sms(cfg.cache.uses_sms() and stage + 1 < cfg.cache.o.total_depth_moe)
+                fc1_groups = cfg.cache.ready_groups(stage, "w1")  # the first layer's w1 arrives in groups of experts
+                if fc1_groups is None or w1.dtype != dtype:
+                    cfg.cache.wait(stage, "w1")
+                    fc1_groups = None
                 before_fc2 = lambda: cfg.cache.wait(stage, "w2")
             else:
                 w1, w2, b1 = fc1_w, fc2_w, fc1_bias
-                before_fc2 = None
+                before_fc2 = fc1_groups = None
             if w1.dtype != dtype or w2.dtype != dtype:            # a cast reads both tensors now
                 if before_fc2 is not None:
                     before_fc2()
@@ -290,7 +294,7 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
             y, st = cfg.backend.moe_forward(x, ids, w1.detach(), w2.detach(), None if b1 is None else b1.detach(),
                                             None if fc2_bias is None else fc2_bias.detach(), cfg.act_id,
                                             act_fn=cfg.activation_fn, route_major=True, need_state=need_state,
-                                            before_fc2=before_fc2)
+                                            before_fc2=before_fc2, **({"fc1_groups": fc1_groups} if fc1_groups else {}))
             if W > 1:
                 cfg.cache.release(stage)
                 cfg.cache.limit_compute_sms(False)

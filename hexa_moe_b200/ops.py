@@ -134,9 +134,10 @@ def combine_rows(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = No
 def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Optional[torch.Tensor] = None,
          epilogue: int = L.EPI_LINEAR, act: int = L.ACT_NONE, aux: Optional[torch.Tensor] = None,
          out: Optional[torch.Tensor] = None, engine: int = L.ENGINE_AUTO, n_out: Optional[int] = None,
-         k: Optional[int] = None, tag: Optional[str] = None) -> torch.Tensor:
+         k: Optional[int] = None, tag: Optional[str] = None, experts: Optional[tuple] = None) -> torch.Tensor:
     """c[row] = a[row] x b[expert(row)] with the fused epilogue.  b: [E, n_out, k] (B_NK) or [E, k, n_out] (B_KN);
-    b may be a view with arbitrary expert / row strides (unit inner stride)."""
+    b may be a view with arbitrary expert / row strides (unit inner stride).  experts = (first, end): only the rows of
+    those experts are computed (the other rows of `out` are left as they are)."""
     if r.align % L.ROW_TILE:
         raise L.HexaError("esmm: routing must be aligned to 128 rows")
     if b.dim() != 3 or b.stride(2) != 1:
@@ -156,12 +157,14 @@ def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Opti
     rows_ = r.num_tokens * r.top_k
     es_ = a.element_size()
     nbytes = es_ * (rows_ * k + r.num_experts * n_out * k + rows_ * n_out * (1 if epilogue == L.EPI_LINEAR else 2))
-    with _Timed("esmm:" + (tag or "epilogue%d" % epilogue), 2.0 * rows_ * n_out * k, float(nbytes)):
-        check(lib().hexa_esmm(ptr(a), _ld(a), ptr(b), b_layout, b.stride(1), b.stride(0), ptr(bias),
-                              0 if bias is None else _ld(bias), ptr(aux), 0 if aux is None else _ld(aux), ptr(out), _ld(out),
-                              ptr(r.tile_expert), ptr(r.pad_offsets), ptr(r.row_token), ptr(r.pair_block), r.num_experts, r.row_capacity,
-                              n_out, k,
-                              dt(a), epilogue, act, engine, stream_of(a)), "hexa_esmm")
+    e0, e1 = (0, r.num_experts) if experts is None else experts
+    share = (e1 - e0) / max(r.num_experts, 1)        # work of a group, taken as its share of the experts
+    with _Timed("esmm:" + (tag or "epilogue%d" % epilogue), 2.0 * rows_ * n_out * k * share, float(nbytes) * share):
+        check(lib().hexa_esmm_experts(ptr(a), _ld(a), ptr(b), b_layout, b.stride(1), b.stride(0), ptr(bias),
+                                      0 if bias is None else _ld(bias), ptr(aux), 0 if aux is None else _ld(aux), ptr(out),
+                                      _ld(out), ptr(r.tile_expert), ptr(r.pad_offsets), ptr(r.row_token), ptr(r.pair_block),
+                                      r.num_experts, r.row_capacity, n_out, k, dt(a), epilogue, act, engine, e0, e1,
+                                      stream_of(a)), "hexa_esmm")
     return out
 
 
@@ -323,10 +326,12 @@ def _f32(t):
 
 
 def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=False, engine=L.ENGINE_AUTO,
-                need_state=True, before_fc2=None):
+                need_state=True, before_fc2=None, fc1_groups=None):
     """y[t] = sum_j fc2(act(fc1(x[t]; e_j)); e_j).  x [T,d]; ids int32 [T,k] ([k,T] if route_major);
     w1 [E,H,d]; w2 [E,H,d_out]; b1 [E,H] / b2 [E,d_out] or None.  before_fc2: optional callable run on the host
-    between the launches of fc1 and fc2 (the caller may enqueue a stream wait for w2 there).
+    between the launches of fc1 and fc2 (the caller may enqueue a stream wait for w2 there).  fc1_groups: optional list of
+    (first expert, end expert, callable) - fc1 is then launched once per group, after calling the group's callable
+    (the caller enqueues the stream wait for that group's fc1 weights there), so the layer starts before all of w1 is in.
     act_id: an _lib.ACT_* id fused into the fc1 epilogue, or -1 to call `act_fn` (any elementwise
     callable) between the two ESMMs.  Returns (y [T,d_out], LayerState)."""
     E = w1.shape[0]
@@ -336,10 +341,18 @@ def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=Fa
     H = w1.shape[1]
     y1 = sorted_buffer(r.row_capacity, H, x.dtype, x.device)
     g = None
+    groups = fc1_groups if fc1_groups else [(0, E, None)]
     if act_id >= 0:
-        h = esmm(xs, w1, L.B_NK, r, b1f, L.EPI_ACT, act_id, aux=y1, engine=engine, tag="fc1_forward_act")
+        h = sorted_buffer(r.row_capacity, H, x.dtype, x.device)
+        for e0, e1, ready in groups:
+            if ready is not None:
+                ready()
+            esmm(xs, w1, L.B_NK, r, b1f, L.EPI_ACT, act_id, aux=y1, out=h, engine=engine, tag="fc1_forward_act", experts=(e0, e1))
     else:
-        esmm(xs, w1, L.B_NK, r, b1f, L.EPI_LINEAR, out=y1, engine=engine, tag="fc1_forward")
+        for e0, e1, ready in groups:
+            if ready is not None:
+                ready()
+            esmm(xs, w1, L.B_NK, r, b1f, L.EPI_LINEAR, out=y1, engine=engine, tag="fc1_forward", experts=(e0, e1))
         if need_state:
             with torch.enable_grad():
                 yy = y1.detach().requires_grad_(True)

@@ -159,6 +159,17 @@ int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout, int64_t l
               const int32_t* pair_block, int num_experts, int64_t row_capacity, int64_t n_out, int64_t k,
               int dtype, int epilogue, int act, int engine, void* stream);
 
+/* hexa_esmm restricted to the rows of experts expert_begin <= e < expert_end; rows of other experts are left untouched.
+ * Launching the layer's first GEMM once per group of experts lets it start on the experts whose weights have arrived
+ * while the remaining weights of the layer are still being gathered from the other ranks (no counterpart in the
+ * reference, which waits for the whole gathered tensor: impls/layers.py:109-124).  The groups of one operator may be
+ * launched in any order and together write exactly what one hexa_esmm call writes. */
+int hexa_esmm_experts(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
+                      const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
+                      const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
+                      const int32_t* pair_block, int num_experts, int64_t row_capacity, int64_t n_out, int64_t k,
+                      int dtype, int epilogue, int act, int engine, int expert_begin, int expert_end, void* stream);
+
 /* ---- ESTMM: replaces task 1 of launch_fused_grad_* (include/hexa_moe.h:74-181),
  *      kernels/fused.py:183-235 (operator definition; the reference kernels mis-handle segments
  *      longer than 16 rows) ----

@@ -16,11 +16,12 @@ def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 
 
-def _worker(rank, world, port, data_centric, proportion, dtype_name, q):
+def _worker(rank, world, port, data_centric, proportion, dtype_name, q, env=None):
     import torch.distributed as dist
     import torch.nn.functional as F
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(env or {})
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
@@ -100,14 +101,14 @@ def _worker(rank, world, port, data_centric, proportion, dtype_name, q):
         dist.destroy_process_group()
 
 
-def _run(data_centric, proportion, dtype_name):
+def _run(data_centric, proportion, dtype_name, env=None):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, data_centric, proportion, dtype_name, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, data_centric, proportion, dtype_name, q, env)) for r in range(2)]
     for p in procs:
         p.start()
     try:
@@ -129,3 +130,15 @@ def test_data_centric_two_gpus(proportion, dtype_name):
 @pytest.mark.parametrize("proportion,dtype_name", [(None, "float32"), ([0.375, 0.625], "bfloat16")])
 def test_model_centric_two_gpus(proportion, dtype_name):
     _run(False, proportion, dtype_name)
+
+
+def test_data_centric_two_gpus_gradients_stored_into_the_owners_buffers():
+    """HEXA_P2P_SCATTER=1: the weight-gradient GEMM stores every hidden slice straight into its owner's receive buffer
+    over NVLink (hexa_estmm_scatter with destinations in the other GPU's memory) instead of writing locally and letting
+    copy engines pull; same gradients as the default path, within the bf16 tolerance against the oracle."""
+    _run(True, None, "bfloat16", env={"HEXA_P2P_SCATTER": "1"})
+
+
+def test_data_centric_two_gpus_gradients_returned_through_autograd():
+    """HEXA_DEFER_GRADS=0 on real devices: backward waits for the side-stream reduction and returns the slices."""
+    _run(True, None, "bfloat16", env={"HEXA_DEFER_GRADS": "0"})
