@@ -6,42 +6,27 @@
 using namespace hexa;
 
 namespace {
-// A kernel on device `dev` is about to store through `ptr`.  Memory of another GPU is reachable only after
-// cudaDeviceEnablePeerAccess from the storing device (access in the opposite direction, which is all that peer
-// copies into this GPU need, does not help), so it is enabled here, once per device pair, or the call is refused.
-int ensure_store_access(const void* ptr, int dev, const char* who) {
-  static unsigned char enabled[64][64];
+// Destinations of hexa_estmm_scatter must live in the calling device's own memory.  Stores from the GEMM kernel into
+// another GPU's memory (IPC-mapped buffers of a peer process) ended in an illegal-address fault in every run that
+// tried them on two B200s - with peer access enabled only towards the calling device, and again with
+// cudaDeviceEnablePeerAccess issued from the storing device - while the same kernel with local destinations is
+// bit-identical to the packed layout.  The cause is not known, so the entry point refuses such pointers.
+int require_local_destination(const void* ptr, int dev, const char* who) {
   cudaPointerAttributes at;
   if (cudaPointerGetAttributes(&at, ptr) != cudaSuccess) {
     (void)cudaGetLastError();
     set_error("%s: cannot classify destination pointer %p", who, ptr);
     return HEXA_ERR_INVALID;
   }
-  if (at.type != cudaMemoryTypeDevice && at.type != cudaMemoryTypeManaged) {
+  if (at.type != cudaMemoryTypeDevice) {
     set_error("%s: destination %p is not device memory", who, ptr);
     return HEXA_ERR_INVALID;
   }
-  const int owner = at.device;
-  if (at.type == cudaMemoryTypeManaged || owner == dev) return HEXA_OK;
-  if (owner < 0 || owner >= 64) {
-    set_error("%s: destination %p belongs to device %d (out of range)", who, ptr, owner);
+  if (at.device != dev) {
+    set_error("%s: destination %p lives on device %d, the call runs on device %d: destinations in another GPU's memory "
+              "are not supported (move the slice with a peer copy instead)", who, ptr, at.device, dev);
     return HEXA_ERR_UNSUPPORTED;
   }
-  if (__atomic_load_n(&enabled[dev][owner], __ATOMIC_ACQUIRE)) return HEXA_OK;
-  int can = 0;
-  if (cudaDeviceCanAccessPeer(&can, dev, owner) != cudaSuccess || !can) {
-    (void)cudaGetLastError();
-    set_error("%s: device %d cannot access the memory of device %d that destination %p lives in", who, dev, owner, ptr);
-    return HEXA_ERR_UNSUPPORTED;
-  }
-  const cudaError_t e = cudaDeviceEnablePeerAccess(owner, 0);
-  if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
-    set_error("%s: cudaDeviceEnablePeerAccess(%d) from device %d failed: %s", who, owner, dev, cudaGetErrorString(e));
-    (void)cudaGetLastError();
-    return HEXA_ERR_UNSUPPORTED;
-  }
-  (void)cudaGetLastError();
-  __atomic_store_n(&enabled[dev][owner], (unsigned char)1, __ATOMIC_RELEASE);
   return HEXA_OK;
 }
 }  // namespace
@@ -138,7 +123,7 @@ extern "C" int hexa_estmm_scatter(const void* p, int64_t ldp, const void* q, int
   HEXA_REQUIRE(dev >= 0 && dev < 64, "hexa_estmm_scatter: device ordinal %d out of range", dev);
   for (int i = 0; i < n_split; ++i) {
     HEXA_REQUIRE(split_out[i], "hexa_estmm_scatter: split_out[%d] is null", i);
-    const int rc = ensure_store_access(split_out[i], dev, "hexa_estmm_scatter");
+    const int rc = require_local_destination(split_out[i], dev, "hexa_estmm_scatter");
     if (rc != HEXA_OK) return rc;
     if (!estmm_tc_supported(p, ldp, q, ldq, split_out[i], ldo, o_estride, 0, n, dtype, out_dtype)) {
       set_error("hexa_estmm_scatter: needs 16-byte aligned pointers and leading dimensions / n that are multiples of 8");

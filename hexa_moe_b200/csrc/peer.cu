@@ -77,6 +77,27 @@ mean_slices_kernel(const T* __restrict__ local, const T* __restrict__ recv, int 
   }
 }
 
+// Blocks of two kernels share an SM only if both run with the same split of the SM's L1 / shared-memory array.  The
+// GEMM kernels this one is meant to run beside take the largest shared-memory carve-out, so the same preference is set
+// here (the kernel itself uses no shared memory); without it the blocks wait for a GEMM kernel to drain.
+template <typename K>
+void prefer_max_shared_carveout(K kernel) {
+  static bool done[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
+  if (!done[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+      (void)cudaGetLastError();
+    done[dev] = true;
+  }
+}
+
+template <typename T, int S, int U>
+void mean_slices_launch_su(const T* l, const T* r, int n_recv, int64_t elems, float scale, T* o, unsigned blocks, cudaStream_t stream) {
+  prefer_max_shared_carveout(mean_slices_kernel<T, S, U>);
+  mean_slices_kernel<T, S, U><<<blocks, 128, 0, stream>>>(l, r, n_recv, elems, scale, o);
+}
+
 template <typename T>
 void mean_slices_launch(const void* local, const void* recv, int n_recv, int64_t elems, float scale, void* out, unsigned blocks,
                         cudaStream_t stream) {
@@ -84,10 +105,10 @@ void mean_slices_launch(const void* local, const void* recv, int n_recv, int64_t
   const T* r = static_cast<const T*>(recv);
   T* o = static_cast<T*>(out);
   switch (n_recv + 1) {
-    case 2: mean_slices_kernel<T, 2, 4><<<blocks, 128, 0, stream>>>(l, r, n_recv, elems, scale, o); break;
-    case 4: mean_slices_kernel<T, 4, 2><<<blocks, 128, 0, stream>>>(l, r, n_recv, elems, scale, o); break;
-    case 8: mean_slices_kernel<T, 8, 1><<<blocks, 128, 0, stream>>>(l, r, n_recv, elems, scale, o); break;
-    default: mean_slices_kernel<T, 0, 1><<<blocks, 128, 0, stream>>>(l, r, n_recv, elems, scale, o); break;
+    case 2: mean_slices_launch_su<T, 2, 4>(l, r, n_recv, elems, scale, o, blocks, stream); break;
+    case 4: mean_slices_launch_su<T, 4, 2>(l, r, n_recv, elems, scale, o, blocks, stream); break;
+    case 8: mean_slices_launch_su<T, 8, 1>(l, r, n_recv, elems, scale, o, blocks, stream); break;
+    default: mean_slices_launch_su<T, 0, 1>(l, r, n_recv, elems, scale, o, blocks, stream); break;
   }
 }
 

@@ -396,9 +396,10 @@ class PipelineSharedCache:
                 ev.record(self.side)
                 slot["ready"][kind] = ev
 
-    def prefetch(self, stage: int, order=("w1", "b1", "w2")):
+    def prefetch(self, stage: int, order=("b1", "w1", "w2")):
         """Start assembling layer `stage` (no-op when out of range or already present).  `order`: which tensors,
-        first needed first (forward: fc1 then fc2; backward: ("w2", "w1"))."""
+        first needed first (forward: fc1's bias - tiny, so that nothing waits for it behind the weights - then fc1, then fc2;
+        backward: ("w2", "w1"))."""
         o = self.o
         if stage < 0 or stage >= o.total_depth_moe or o.world_size == 1:
             return
@@ -446,7 +447,7 @@ class PipelineSharedCache:
             return None
         return [(e0, e1, (lambda ev=ev: self._compute_wait(ev, "wait." + kind))) for e0, e1, ev in groups]
 
-    def get(self, stage: int, order=("w1", "b1", "w2"), wait=("w1", "b1", "w2")):
+    def get(self, stage: int, order=("b1", "w1", "w2"), wait=("w1", "b1", "w2")):
         """Full (w1 [E,H,d_in], w2 [E,H,d_out], b1 [E,H] | None) of layer `stage`.  Starts the gather if needed and
         orders the current stream after the tensors named in `wait`; call wait() for the others before using them."""
         self.prefetch(stage, order)
@@ -566,18 +567,7 @@ class PipelineSharedCache:
         W, E, loc = o.world_size, o.num_global_experts, o.local_dim_list[stage]
         d = o.input_dim_list_moe[stage] if which == "fc1" else o.output_dim_list_moe[stage]
         self._compute_wait(self._red["free"][(which, stage % 2)], "wait.grad_buffer_free")
-        if self._scatter():
-            # receive layout: slot r of every rank's buffer holds rank r's contribution to that rank's hidden slice, and
-            # ESTMM stores each slice straight into its owner's buffer (hexa_estmm_scatter): a list of W destinations
-            n, me = E * loc * d, o.local_rank
-            return [self._red["peer_grad"][w][which][stage % 2][me * n: (me + 1) * n].view(E, loc, d) for w in range(W)]
         return self._red["grad"][which][stage % 2][: W * E * loc * d].view(W, E, loc, d)
-
-    def _scatter(self) -> bool:
-        """Weight gradients travel by the GEMM's own stores into the owners' buffers (HEXA_P2P_SCATTER=1) instead of
-        being written locally and pulled by copy engines."""
-        return (os.environ.get("HEXA_P2P_SCATTER", "0") == "1" and self._red not in (None, False)
-                and self._red["flags"].is_cuda and self._red["grad"]["fc1"][0].dtype in (torch.float16, torch.bfloat16))
 
     def _reduce_peer(self, which: str, stage: int, out):
         """Side stream: out[E, loc, d] = mean over ranks of their packed gradient's slice for this rank."""
@@ -588,18 +578,6 @@ class PipelineSharedCache:
         par = stage % 2
         with self._span("reduce.grads_complete_barrier", "side", self.side):
             self._peer_barrier("gradients-complete barrier of %s, layer %d" % (which, stage))
-        if self._scatter():
-            # every rank's contribution to this rank's slice already sits in this rank's buffer, slot = source rank:
-            # add the W slots in rank order (the same order on every rank)
-            buf = red["grad"][which][par][: W * n].view(W, n)
-            with self._span("reduce.mean_kernel", "side", self.side):
-                _ops.mean_slices(buf[0], buf[1:], W - 1, W, out.view(-1))
-            with self._span("reduce.readers_done_barrier", "side", self.side):
-                self._peer_barrier("readers-done barrier of %s, layer %d" % (which, stage))
-            ev = torch.cuda.Event()
-            ev.record(self.side)
-            red["free"][(which, par)] = ev
-            return
         if red["recv"] is None:      # allocated on the side stream, the only stream that uses it
             red["recv"] = torch.empty(red["recv_elems"], device=out.device, dtype=out.dtype)
         recv = red["recv"][: (W - 1) * n].view(W - 1, n)
@@ -639,9 +617,7 @@ class PipelineSharedCache:
         targets = [t for t in targets if t[0] is not None and t[1] is not None]
 
         peer_out = None
-        if packed and self._red not in (None, False) and isinstance(dw, (list, tuple)):
-            peer_out = dw[rank].new_empty(tuple(dw[rank].shape))      # scatter mode: dw is the list of per-owner destinations
-        elif packed and self._red not in (None, False) and dw is not None and dw.dim() == 4:
+        if packed and self._red not in (None, False) and dw is not None and dw.dim() == 4:
             # allocated on the compute stream: it becomes the parameter's .grad
             peer_out = dw.new_empty(tuple(dw.shape[1:]))
 
@@ -670,7 +646,7 @@ class PipelineSharedCache:
                 ev.record(self.side)
             # the inputs stay referenced until the flush (after the compute stream has waited for `ev`), so their
             # memory cannot be handed out again while the side stream still reads it
-            keep = [g for _, g, _ in targets if not isinstance(g, (list, tuple))]
+            keep = [g for _, g, _ in targets]
         if not defer:
             self._compute_wait(ev, "wait.reduction_inline")
             for _, g in outs:

@@ -199,12 +199,11 @@ int hexa_estmm(const void* p, int64_t ldp, const void* q, int64_t ldq, const int
  * gradient through torch.distributed, impls/layers.py:431-474): output row i of expert e is written at
  *   split_out[i / m_split] + e*o_estride + (i % m_split)*ldo            (elements of out_dtype)
  * split_out is a HOST array of n_split = ceil(m / m_split) <= 16 device pointers (copied at the call).  Meant for
- * laying a weight gradient out per owner of a hidden slice without a packing pass.  A destination may be another
- * GPU's memory (the transfer of a reduce-scatter done by the GEMM's own stores): stores from the calling device need
- * peer access in that direction, which peer copies INTO the calling device do not establish, so the entry point
- * enables it itself (cudaDeviceEnablePeerAccess, once per device pair) and returns HEXA_ERR_UNSUPPORTED when the
- * devices cannot reach each other, HEXA_ERR_INVALID for a destination that is not device memory.  (An earlier
- * version left this to the caller and faulted with an illegal address on remote destinations.)
+ * laying a weight gradient out per owner of a hidden slice without a packing pass.  Every destination must be memory of
+ * the calling device: a pointer into another GPU's memory is refused with HEXA_ERR_UNSUPPORTED (anything that is not
+ * device memory with HEXA_ERR_INVALID).  Stores of this kernel into a peer's IPC-mapped buffer faulted with an illegal
+ * address on two B200s in every attempt, with and without cudaDeviceEnablePeerAccess from the storing device; the
+ * cause is not known, so the transfer of the reduce-scatter stays with the copy engines.
  * 16-bit inputs only (the tcgen05 kernel); the destination is overwritten (beta = 0). */
 int hexa_estmm_scatter(const void* p, int64_t ldp, const void* q, int64_t ldq, const int32_t* pad_offsets,
                        int num_experts, int64_t row_capacity, int64_t m, int64_t n, void* const* split_out, int n_split,

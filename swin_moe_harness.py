@@ -37,6 +37,24 @@ def shifted_window_mask(hw: int, w: int, shift: int) -> torch.Tensor:
     return (per_window.unsqueeze(1) != per_window.unsqueeze(2)).float() * -100.0
 
 
+def _attention(q, k, v, mask):
+    """scaled_dot_product_attention with an additive mask.  On CUDA the fused backends that take a bias are preferred in
+    the order given by SWIN_SDPA_BACKENDS (default "cudnn,efficient,math"); whichever accepts the shapes runs."""
+    if not q.is_cuda:
+        return F.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+    import os
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+    names = {"cudnn": SDPBackend.CUDNN_ATTENTION, "efficient": SDPBackend.EFFICIENT_ATTENTION, "math": SDPBackend.MATH,
+             "flash": SDPBackend.FLASH_ATTENTION}
+    order = [names[n] for n in os.environ.get("SWIN_SDPA_BACKENDS", "cudnn,efficient,math").split(",") if n in names]
+    try:
+        with sdpa_kernel(order, set_priority=True):
+            return F.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+    except TypeError:        # an older sdpa_kernel without set_priority
+        with sdpa_kernel(order):
+            return F.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+
+
 class WindowAttention(nn.Module):
     def __init__(self, dim: int, heads: int, window: int, shift: int):
         super().__init__()
@@ -94,7 +112,7 @@ class WindowAttention(nn.Module):
             q, k, v = (t.reshape(B, nw * nw * self.heads, n, hd) for t in qkv)
         else:
             q, k, v = (t.reshape(B * nw * nw, self.heads, n, hd) for t in qkv)
-        o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+        o = _attention(q, k, v, mask)
         o = o.view(B, nw * nw, self.heads, n, hd).transpose(2, 3).reshape(B, nw, nw, w, w, C)
         o = self.proj(o).permute(0, 1, 3, 2, 4, 5).reshape(B, hw, hw, C)
         if shifted:

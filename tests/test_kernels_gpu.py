@@ -354,6 +354,35 @@ def test_layer_forward_backward(ops, dtype, E, k, d, H, act):
         assert e < tol, (name, e)
 
 
+@pytest.mark.parametrize("dtype,n_out", [(torch.bfloat16, 512), (torch.bfloat16, 128), (torch.float32, 96)])
+def test_esmm_by_expert_groups_equals_one_launch(ops, dtype, n_out):
+    """hexa_esmm_experts: launching the operator once per group of experts (any order) writes exactly what one launch
+    over all experts writes, and a group's launch leaves the rows of other experts untouched."""
+    Lb = L()
+    T, k, E, d = 3000, 2, 7, 256
+    ids = make_ids(T, k, E, 4, skew=True, empty=(3,))
+    r = ops.route(ids.cuda(), E)
+    g = torch.Generator().manual_seed(n_out)
+    xs = ops.gather_rows(torch.randn(T, d, generator=g).to(dtype).cuda(), r)
+    w = (torch.randn(E, n_out, d, generator=g) / 16).to(dtype).cuda()
+    b = (torch.randn(E, n_out, generator=g) * 0.1).cuda()
+    n_pad = int(r.pad_offsets[-1])
+    full_aux = torch.zeros(r.row_capacity, n_out, dtype=dtype, device="cuda")
+    full = ops.esmm(xs, w, Lb.B_NK, r, b, Lb.EPI_ACT, Lb.ACT_GELU, aux=full_aux)
+    out = torch.full((r.row_capacity, n_out), 7.0, dtype=dtype, device="cuda")
+    aux = torch.full_like(out, 7.0)
+    ops.esmm(xs, w, Lb.B_NK, r, b, Lb.EPI_ACT, Lb.ACT_GELU, aux=aux, out=out, experts=(4, 7))
+    lo = int(r.pad_offsets[4])
+    assert (out[:lo] == 7.0).all() and (aux[:lo] == 7.0).all()                    # experts 0..3 untouched
+    assert torch.equal(out[lo:n_pad], full[lo:n_pad]) and torch.equal(aux[lo:n_pad], full_aux[lo:n_pad])
+    for e0, e1 in ((2, 4), (0, 2)):                                              # the remaining groups, out of order
+        ops.esmm(xs, w, Lb.B_NK, r, b, Lb.EPI_ACT, Lb.ACT_GELU, aux=aux, out=out, experts=(e0, e1))
+    assert torch.equal(out[:n_pad], full[:n_pad]) and torch.equal(aux[:n_pad], full_aux[:n_pad])
+    ops.esmm(xs, w, Lb.B_NK, r, b, out=out, experts=(3, 3))                        # an empty range launches nothing
+    with pytest.raises(Lb.HexaError):
+        ops.esmm(xs, w, Lb.B_NK, r, b, out=out, experts=(5, 9))
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
 @pytest.mark.parametrize("n_recv", [0, 1, 2, 3, 5, 7])
 def test_mean_slices(ops, dtype, n_recv):

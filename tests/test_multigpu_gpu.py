@@ -132,13 +132,27 @@ def test_model_centric_two_gpus(proportion, dtype_name):
     _run(False, proportion, dtype_name)
 
 
-def test_data_centric_two_gpus_gradients_stored_into_the_owners_buffers():
-    """HEXA_P2P_SCATTER=1: the weight-gradient GEMM stores every hidden slice straight into its owner's receive buffer
-    over NVLink (hexa_estmm_scatter with destinations in the other GPU's memory) instead of writing locally and letting
-    copy engines pull; same gradients as the default path, within the bf16 tolerance against the oracle."""
-    _run(True, None, "bfloat16", env={"HEXA_P2P_SCATTER": "1"})
-
-
 def test_data_centric_two_gpus_gradients_returned_through_autograd():
     """HEXA_DEFER_GRADS=0 on real devices: backward waits for the side-stream reduction and returns the slices."""
     _run(True, None, "bfloat16", env={"HEXA_DEFER_GRADS": "0"})
+
+
+def test_weight_gradient_stores_into_another_gpus_memory_are_refused():
+    """hexa_estmm_scatter takes destinations in the calling GPU's memory only; a pointer into a peer's memory is
+    refused before anything is launched (stores of that kernel into peer memory are not supported)."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    sys.path.insert(0, ROOT)
+    from hexa_moe_b200 import _lib as L, ops
+    torch.cuda.set_device(0)
+    T, k, E, M, N = 600, 1, 2, 256, 128
+    ids = torch.randint(0, E, (T, k), dtype=torch.int32, device="cuda:0")
+    r = ops.route(ids, E)
+    p = ops.gather_rows(torch.randn(T, M, device="cuda:0").bfloat16(), r)
+    q = ops.gather_rows(torch.randn(T, N, device="cuda:0").bfloat16(), r)
+    local = torch.zeros(E, M // 2, N, dtype=torch.bfloat16, device="cuda:0")
+    remote = torch.zeros(E, M // 2, N, dtype=torch.bfloat16, device="cuda:1")
+    with pytest.raises(L.HexaError, match="another GPU"):
+        ops.estmm(p, q, r, ranks=2, out=[local, remote])
+    torch.cuda.synchronize()
+    assert (local == 0).all() and (remote == 0).all()          # refused before any launch
