@@ -376,9 +376,12 @@ def run_swin(args, dev, rank, world, timed_factory=None):
     if sampler:
         sampler.start()
     l0 = ops.LAUNCHES
+    ops.PROFILE = []
     ms = timed(lambda: step(imgs_dev), args.steps)
+    prof, ops.PROFILE = ops.PROFILE, None
     launches = ops.LAUNCHES - l0
     clocks = sampler.stop() if sampler else None
+    lib_ms = sum(e0.elapsed_time(e1) for _n, e0, e1, _w, _b in prof) / args.steps      # this library's kernels, per step
     step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
     parity = multi_gpu_parity(rank, world, dev, True, None) if world > 1 else None
@@ -392,6 +395,10 @@ def run_swin(args, dev, rank, world, timed_factory=None):
                                 note="window attention with relative position bias and shifted-window mask; stock PyTorch "
                                      "attention blocks around one shared MoE_Cascaded"),
                     moe_layer_tokens_per_s=moe_tokens / (ms * 1e-3), parity=parity,
+                    library_kernel_ms_per_step=round(lib_ms, 3),
+                    library_note="moe_layer_tokens_per_s divides the MoE-layer tokens of a step by the whole step; "
+                                 "library_kernel_ms_per_step is the part of the step spent in this library's kernels (MoE "
+                                 "layers and the dense FFNs of model dim >= 512), the rest is stock PyTorch attention",
                     e2e=dict(value=args.images * world / (ms_e2e * 1e-3), unit="images/s", ms_per_step=ms_e2e,
                              h2d_bytes_per_step=imgs_host.numel() * 2, d2h_bytes_per_step=4),
                     gpu_launches=launches, clocks=clocks)
