@@ -303,13 +303,19 @@ template <int BN, int CTAS, int EW, int MODE> struct Cfg {
   static constexpr int kThreads = 32 * (2 + EW);
   // ESTMM stores from registers and needs no staging tile: its ring gets the space (one more 32 KB slot), which is what
   // a loop bounded by the latency of a ring slot's round trip (MMA done -> slot refilled) converts into throughput
-  static constexpr int kStages = (BN == 256 && CTAS == 1) ? 4 : (MODE == ESTMM ? 7 : 6);
+#ifndef HEXA_TC_RING_SLOTS      // build-time override for experiments with the ring depth (0 = the defaults below)
+#define HEXA_TC_RING_SLOTS 0
+#endif
+#ifndef HEXA_TC_SMEM_SLACK      // bytes kept for aligning the dynamic shared memory base to 1 KB by hand
+#define HEXA_TC_SMEM_SLACK 1024
+#endif
+  static constexpr int kStages = (BN == 256 && CTAS == 1) ? 4 : (HEXA_TC_RING_SLOTS ? HEXA_TC_RING_SLOTS : (MODE == ESTMM ? 7 : 6));
   static constexpr uint32_t kBBytes = (BN / CTAS) * BLOCK_K * 2;   // this CTA's share of the B tile
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators; 256 or 512, a power of two
   static constexpr uint32_t kStoreBufBytes = 128 * 64;   // [128 rows x 32 16-bit columns]
   static constexpr uint32_t kStoreBytes = MODE == ESTMM ? 0 : (EW / 4) * kStoreBufBytes;  // one buffer per group of four epilogue warps
-  static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + kStoreBytes + 256 /*barriers*/;
+  static constexpr size_t kSmemBytes = HEXA_TC_SMEM_SLACK + (size_t)kStages * kStageBytes + kStoreBytes + 256 /*barriers*/;
   static_assert(kSmemBytes <= 232448, "more shared memory than one CTA can have (227 KB)");
 };
 
@@ -438,8 +444,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr int kEpiWarps = EW;
   constexpr int kStages = C::kStages;
   constexpr int BNH = BN / CTAS;          // B columns this CTA loads
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  if (HEXA_TC_SMEM_SLACK < 1024 && smem != smem_raw) {      // without slack the base itself must be 1 KB aligned
+    if (threadIdx.x == 0) report_status(p.status, 9);
+    return;                                                  // uniform: every thread of every CTA sees the same base offset
+  }
   uint8_t* store_bufs = smem + (size_t)kStages * C::kStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(store_bufs + C::kStoreBytes);
   uint64_t* full = bars;                  // [kStages]  producers -> MMA     (used in the leader CTA)

@@ -4,6 +4,7 @@
 //   hexa_mean_slices         out = (local + sum of n received slices) / world, fp32 accumulation: the reduction
 //                            step of a reduce-scatter whose transfers were plain peer copies
 #include <cuda.h>
+#include <stdlib.h>
 #include <cudaTypedefs.h>
 
 #include "hexa_common.cuh"
@@ -11,15 +12,21 @@
 namespace hexa {
 namespace {
 
-// The kernel runs on a side stream next to the persistent GEMM kernels, which leave room for one small block per SM
-// (about 10K registers and no shared memory), so its bandwidth comes from loads in flight per thread, not from
-// occupancy: a thread fetches the same 16-byte vector of all S slices for U positions at once (S * U = 8 independent
-// loads) before it adds anything.  S = n_recv + 1 when that is 2, 4 or 8; other counts take the generic loop.
+// The kernel runs on a side stream beside the persistent GEMM kernels, and what it may use is what such a kernel's CTA
+// leaves of an SM.  The register file is split over the four sub-partitions (16K registers each); the GEMM CTA puts
+// five warps of 96 registers on two of them (its TMA-producer and MMA-issuer warps share sub-partitions 0 and 1 with
+// epilogue warps), which leaves exactly 1024 registers there: one warp of 32 registers per thread.  A block of this
+// kernel is therefore four warps (one per sub-partition) compiled to at most 32 registers; with more, its blocks are
+// not scheduled until a GEMM kernel has drained (measured: a launch then takes as long as a GEMM, 5-8 ms instead of
+// under 1 ms).  Within 32 registers a thread keeps four independent 16-byte loads in flight: the same vector of four
+// slices (or of two slices at two positions) before anything is added.  S = n_recv + 1 when that is 2, 4 or 8; other
+// slice counts take the generic loop.
 template <typename T, int S, int U>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 16)
 mean_slices_kernel(const T* __restrict__ local, const T* __restrict__ recv, int n_recv, int64_t elems, float scale,
                    T* __restrict__ out) {
   constexpr int V = 16 / sizeof(T);
+  constexpr int B = S > 4 ? 4 : (S > 0 ? S : 1);      // slices loaded together
   const int64_t nvec = elems / V;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const uint4* loc4 = reinterpret_cast<const uint4*>(local);
@@ -28,30 +35,37 @@ mean_slices_kernel(const T* __restrict__ local, const T* __restrict__ recv, int 
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (S > 0) {
     for (; i + (U - 1) * stride < nvec; i += U * stride) {
-      uint4 raw[U][S > 0 ? S : 1];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        raw[u][0] = __ldg(loc4 + i + u * stride);
+      for (int u0 = 0; u0 < U; u0 += (B == 2 ? 2 : 1)) {
+        constexpr int UB = B == 2 ? 2 : 1;             // positions handled together (two when only two slices exist)
+        float acc[UB][V];
 #pragma unroll
-        for (int s = 1; s < S; ++s) raw[u][s] = __ldg(rcv4 + (int64_t)(s - 1) * nvec + i + u * stride);
-      }
+        for (int s0 = 0; s0 < S; s0 += B) {
+          uint4 raw[UB][B];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        float acc[V];
-        const T* v0 = reinterpret_cast<const T*>(&raw[u][0]);
+          for (int u = 0; u < UB; ++u)
 #pragma unroll
-        for (int j = 0; j < V; ++j) acc[j] = to_f32<T>(v0[j]);
+            for (int s = 0; s < B; ++s) {
+              const int64_t pos = i + (u0 + u) * stride;
+              raw[u][s] = (s0 + s == 0) ? __ldg(loc4 + pos) : __ldg(rcv4 + (int64_t)(s0 + s - 1) * nvec + pos);
+            }
 #pragma unroll
-        for (int s = 1; s < S; ++s) {           // fixed order: local, then the received slices by index
-          const T* v = reinterpret_cast<const T*>(&raw[u][s]);
+          for (int u = 0; u < UB; ++u)
 #pragma unroll
-          for (int j = 0; j < V; ++j) acc[j] += to_f32<T>(v[j]);
+            for (int s = 0; s < B; ++s) {              // fixed order: local, then the received slices by index
+              const T* v = reinterpret_cast<const T*>(&raw[u][s]);
+#pragma unroll
+              for (int j = 0; j < V; ++j) acc[u][j] = (s0 + s == 0) ? to_f32<T>(v[j]) : acc[u][j] + to_f32<T>(v[j]);
+            }
         }
-        uint4 o;
-        T* ov = reinterpret_cast<T*>(&o);
 #pragma unroll
-        for (int j = 0; j < V; ++j) ov[j] = from_f32<T>(acc[j] * scale);
-        out4[i + u * stride] = o;
+        for (int u = 0; u < UB; ++u) {
+          uint4 o;
+          T* ov = reinterpret_cast<T*>(&o);
+#pragma unroll
+          for (int j = 0; j < V; ++j) ov[j] = from_f32<T>(acc[u][j] * scale);
+          out4[i + (u0 + u) * stride] = o;
+        }
       }
     }
   }
@@ -77,6 +91,13 @@ mean_slices_kernel(const T* __restrict__ local, const T* __restrict__ recv, int 
   }
 }
 
+// Grid size in multiples of the SM count (A/B switch HEXA_MEAN_BLOCKS_PER_SM, read at every call; default 4).
+int mean_env(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : dflt;
+}
+constexpr int kMeanThreads = 128;
+
 // Blocks of two kernels share an SM only if both run with the same split of the SM's L1 / shared-memory array.  The
 // GEMM kernels this one is meant to run beside take the largest shared-memory carve-out, so the same preference is set
 // here (the kernel itself uses no shared memory); without it the blocks wait for a GEMM kernel to drain.
@@ -95,7 +116,7 @@ void prefer_max_shared_carveout(K kernel) {
 template <typename T, int S, int U>
 void mean_slices_launch_su(const T* l, const T* r, int n_recv, int64_t elems, float scale, T* o, unsigned blocks, cudaStream_t stream) {
   prefer_max_shared_carveout(mean_slices_kernel<T, S, U>);
-  mean_slices_kernel<T, S, U><<<blocks, 128, 0, stream>>>(l, r, n_recv, elems, scale, o);
+  mean_slices_kernel<T, S, U><<<blocks, kMeanThreads, 0, stream>>>(l, r, n_recv, elems, scale, o);
 }
 
 template <typename T>
@@ -105,8 +126,8 @@ void mean_slices_launch(const void* local, const void* recv, int n_recv, int64_t
   const T* r = static_cast<const T*>(recv);
   T* o = static_cast<T*>(out);
   switch (n_recv + 1) {
-    case 2: mean_slices_launch_su<T, 2, 4>(l, r, n_recv, elems, scale, o, blocks, stream); break;
-    case 4: mean_slices_launch_su<T, 4, 2>(l, r, n_recv, elems, scale, o, blocks, stream); break;
+    case 2: mean_slices_launch_su<T, 2, 2>(l, r, n_recv, elems, scale, o, blocks, stream); break;
+    case 4: mean_slices_launch_su<T, 4, 1>(l, r, n_recv, elems, scale, o, blocks, stream); break;
     case 8: mean_slices_launch_su<T, 8, 1>(l, r, n_recv, elems, scale, o, blocks, stream); break;
     default: mean_slices_launch_su<T, 0, 1>(l, r, n_recv, elems, scale, o, blocks, stream); break;
   }
@@ -148,8 +169,10 @@ extern "C" int hexa_mean_slices(const void* local, const void* recv, int n_recv,
   HEXA_REQUIRE(elems % V == 0, "hexa_mean_slices: element count must be a multiple of %d", V);
   if (elems == 0) return HEXA_OK;
   const float scale = 1.0f / (float)world;
-  int64_t blocks = ceil_div(elems / V, 128 * 8);
-  const int64_t cap = (int64_t)sm_count() * 2;      // at most two waves of one-block-per-SM residency
+  int64_t blocks = ceil_div(elems / V, kMeanThreads * 4);
+  int per_sm = mean_env("HEXA_MEAN_BLOCKS_PER_SM", 4);
+  if (per_sm < 1) per_sm = 1;
+  const int64_t cap = (int64_t)sm_count() * per_sm;   // a few waves of one-block-per-SM residency beside a GEMM kernel
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   switch (dtype) {
