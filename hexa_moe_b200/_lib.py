@@ -56,6 +56,8 @@ SIGNATURES = {
     "hexa_gate_workspace_bytes": (sz, []),
     "hexa_gate_topk": (ci, [vp, i64, i64, ci, ci, vp, vp, vp, vp, vp, sz, vp]),
     "hexa_gate_loss_grad": (ci, [vp, i64, i64, ci, vp, vp, vp, i64, vp]),
+    "hexa_gate_topk_load_importance": (ci, [vp, vp, i64, i64, ci, ci, C.c_float, vp, vp, vp, vp, vp, sz, vp]),
+    "hexa_gate_load_importance_grad": (ci, [vp, vp, i64, i64, ci, ci, C.c_float, vp, vp, vp, vp, i64, vp]),
     "hexa_ess_static_capacity_bytes": (sz, []),
     "hexa_ess_static": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, ci, vp]),
 }

@@ -176,6 +176,173 @@ gate_loss_grad_kernel(const float* __restrict__ logits, int64_t ld, int64_t T, i
   }
 }
 
+
+// ---- the load-importance loss (reference impls/losses.py:21-43) -------------------------------------------------------
+//   importance_e = sum_t softmax(logits)[t,e]                          (clean logits)
+//   load_e       = sum_t Phi((softmax(logits)[t,e] - thr_t) / sigma)   thr_t = the k-th largest NOISY logit of token t,
+//                                                                      sigma = gate_noise / E  (the reference compares a
+//                                                                      score with a logit: kept as it is)
+//   loss         = (cv2(importance) + cv2(load)) / 2,   cv2(v) = var(v) / (mean(v)^2 + 1e-10), var unbiased
+// The top-k ids are those of the noisy logits (softmax is monotonic, so they equal torch.topk of softmax(noisy)).
+__device__ __forceinline__ float normal_cdf(float z) { return 0.5f * (1.f + erff(z * 0.70710678118654752f)); }
+
+// k-th pick of one token's noisy logits held as v[VPT] per lane; writes the ids, returns the last picked value.
+template <int VPT>
+__device__ __forceinline__ float warp_topk(const float (&v)[VPT], int E, int k, int lane, int32_t* __restrict__ ids, int64_t T,
+                                           int64_t t, int* last_id) {
+  unsigned int taken = 0;
+  float thr = 0.f;
+  int bi_last = 0;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = lane + 32 * i;
+      if (c < E && !((taken >> i) & 1u)) {
+        const float x = v[i] == v[i] ? v[i] : -INFINITY;
+        if (bi == 0x7fffffff || x > best) { best = x; bi = c; }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const bool valid = (unsigned)bi < (unsigned)E;
+    if (valid && (bi & 31) == lane) taken |= 1u << (bi >> 5);
+    if (lane == 0 && ids) ids[(int64_t)j * T + t] = valid ? bi : -1;
+    thr = best;
+    bi_last = valid ? bi : -1;
+  }
+  *last_id = bi_last;
+  return thr;
+}
+
+// cv2 of an [E] vector and its gradient factors, computed by one warp (every warp that needs them recomputes them:
+// E <= 512 values).  Returns mean and var through references.
+__device__ __forceinline__ void warp_mean_var(const float* __restrict__ v, int E, int lane, float& mean, float& var) {
+  float s = 0.f;
+  for (int e = lane; e < E; e += 32) s += __ldcg(v + e);
+  mean = warp_sum(s) / (float)E;
+  float q = 0.f;
+  for (int e = lane; e < E; e += 32) { const float d = __ldcg(v + e) - mean; q += d * d; }
+  var = warp_sum(q) / (float)(E - 1);
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(kGateThreads)
+gate_topk_li_kernel(const float* __restrict__ logits, const float* __restrict__ noisy, int64_t ld, int64_t T, int E, int k,
+                    float inv_sigma, int32_t* __restrict__ ids, float* __restrict__ importance, float* __restrict__ load,
+                    float* __restrict__ loss, unsigned int* __restrict__ ticket, float* __restrict__ partial) {
+  __shared__ float sum_w[kGateWarps][2 * 32 * VPT];
+  __shared__ bool last_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t warp0 = (int64_t)blockIdx.x * kGateWarps + warp;
+  const int64_t nwarps = (int64_t)gridDim.x * kGateWarps;
+  float imp[VPT], ld_acc[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) { imp[i] = 0.f; ld_acc[i] = 0.f; }
+  for (int64_t t = warp0; t < T; t += nwarps) {
+    float s[VPT], v[VPT];
+    warp_softmax<VPT>(logits + t * ld, E, lane, s);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) { const int c = lane + 32 * i; v[i] = c < E ? __ldg(noisy + t * ld + c) : -INFINITY; }
+    int last_id;
+    const float thr = warp_topk<VPT>(v, E, k, lane, ids, T, t, &last_id);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      if (lane + 32 * i < E) { imp[i] += s[i]; ld_acc[i] += normal_cdf((s[i] - thr) * inv_sigma); }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) { sum_w[warp][lane + 32 * i] = imp[i]; sum_w[warp][32 * VPT + lane + 32 * i] = ld_acc[i]; }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {       // per-block partial rows, warps added in index order
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int w = 0; w < kGateWarps; ++w) { a += sum_w[w][e]; b += sum_w[w][32 * VPT + e]; }
+    partial[(int64_t)blockIdx.x * 2 * E + e] = a;
+    partial[(int64_t)blockIdx.x * 2 * E + E + e] = b;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last_s = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {       // blocks added in index order
+    float a = 0.f, b = 0.f;
+    for (unsigned blk = 0; blk < gridDim.x; ++blk) {
+      a += __ldcg(partial + (int64_t)blk * 2 * E + e);
+      b += __ldcg(partial + (int64_t)blk * 2 * E + E + e);
+    }
+    importance[e] = a;
+    load[e] = b;
+  }
+  __threadfence();
+  __syncthreads();
+  if (warp == 0) {
+    float mi, vi, ml, vl;
+    warp_mean_var(importance, E, lane, mi, vi);
+    warp_mean_var(load, E, lane, ml, vl);
+    if (lane == 0) loss[0] = 0.5f * (vi / (mi * mi + 1e-10f) + vl / (ml * ml + 1e-10f));
+  }
+}
+
+// d loss / d logits for gate_topk_li_kernel's loss, times dloss[0].  With g_i = d loss / d importance and g_l = d loss /
+// d load (from the forward's totals), pdf_e = phi(z_e) / sigma:
+//   d s_e = g_i[e] + g_l[e] pdf_e ;  d thr = - sum_e g_l[e] pdf_e  (reaches the clean logit of the k-th choice: the noise is a constant)
+//   d logits_e = s_e (d s_e - sum_e' s_e' d s_e') + [e = k-th choice] d thr
+template <int VPT>
+__global__ void __launch_bounds__(kGateThreads)
+gate_li_grad_kernel(const float* __restrict__ logits, const float* __restrict__ noisy, int64_t ld, int64_t T, int E, int k,
+                    float inv_sigma, const float* __restrict__ importance, const float* __restrict__ load,
+                    const float* __restrict__ dloss, float* __restrict__ dlogits, int64_t ldd) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (int64_t)blockIdx.x * kGateWarps + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * kGateWarps;
+  float mi, vi, ml, vl;
+  warp_mean_var(importance, E, lane, mi, vi);
+  warp_mean_var(load, E, lane, ml, vl);
+  const float up = 0.5f * __ldg(dloss);
+  const float di = mi * mi + 1e-10f, dl = ml * ml + 1e-10f;
+  float gi[VPT], gl[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = lane + 32 * i;
+    // d cv2 / d v_e = 2 (v_e - mean) / ((E-1) den) - var * 2 mean / (E den^2)
+    gi[i] = c < E ? up * (2.f * (__ldg(importance + c) - mi) / ((float)(E - 1) * di) - vi * 2.f * mi / ((float)E * di * di)) : 0.f;
+    gl[i] = c < E ? up * (2.f * (__ldg(load + c) - ml) / ((float)(E - 1) * dl) - vl * 2.f * ml / ((float)E * dl * dl)) : 0.f;
+  }
+  for (int64_t t = warp0; t < T; t += nwarps) {
+    float s[VPT], v[VPT];
+    warp_softmax<VPT>(logits + t * ld, E, lane, s);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) { const int c = lane + 32 * i; v[i] = c < E ? __ldg(noisy + t * ld + c) : -INFINITY; }
+    int last_id;
+    const float thr = warp_topk<VPT>(v, E, k, lane, nullptr, T, t, &last_id);
+    float ds[VPT];
+    float dthr = 0.f, dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const float z = (s[i] - thr) * inv_sigma;
+      const float pdf = (lane + 32 * i) < E ? 0.3989422804014327f * expf(-0.5f * z * z) * inv_sigma : 0.f;
+      ds[i] = gi[i] + gl[i] * pdf;
+      dthr -= gl[i] * pdf;
+      dot += s[i] * ds[i];
+    }
+    dthr = warp_sum(dthr);
+    dot = warp_sum(dot);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = lane + 32 * i;
+      if (c < E) dlogits[t * ldd + c] = s[i] * (ds[i] - dot) + (c == last_id ? dthr : 0.f);
+    }
+  }
+}
+
 int gate_grid(int64_t T) {
   const int64_t want = ceil_div(T, kGateThreads / 32);
   int64_t cap = (int64_t)sm_count() * 4;
@@ -245,5 +412,67 @@ extern "C" int hexa_gate_loss_grad(const float* logits, int64_t ld, int64_t num_
   else HEXA_GATE_BWD(16);
 #undef HEXA_GATE_BWD
   HEXA_LAUNCH_CHECK("gate_loss_grad_kernel");
+  return HEXA_OK;
+}
+
+extern "C" int hexa_gate_topk_load_importance(const float* logits, const float* logits_w_noise, int64_t ld, int64_t num_tokens,
+                                              int num_experts, int top_k, float sigma, int32_t* ids, float* importance,
+                                              float* load, float* loss, void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  HEXA_REQUIRE(num_tokens >= 0 && num_experts >= 1 && num_experts <= kGateMaxExperts,
+               "hexa_gate_topk_load_importance: needs 1 <= experts <= %d (got %d)", kGateMaxExperts, num_experts);
+  HEXA_REQUIRE(top_k >= 1 && top_k <= num_experts, "hexa_gate_topk_load_importance: top_k %d out of range for %d experts", top_k, num_experts);
+  HEXA_REQUIRE(sigma > 0.f, "hexa_gate_topk_load_importance: sigma (gate_noise / experts) must be > 0");
+  HEXA_REQUIRE(importance && load && loss && workspace && workspace_bytes >= hexa_gate_workspace_bytes() && aligned16(workspace),
+               "hexa_gate_topk_load_importance: null output, or workspace smaller than hexa_gate_workspace_bytes() or not 16-byte aligned");
+  HEXA_REQUIRE(num_tokens == 0 || (logits && logits_w_noise && ids && ld >= num_experts),
+               "hexa_gate_topk_load_importance: null logits/ids or ld < experts");
+  HEXA_CUDA(cudaMemsetAsync(importance, 0, sizeof(float) * num_experts, stream));
+  HEXA_CUDA(cudaMemsetAsync(load, 0, sizeof(float) * num_experts, stream));
+  HEXA_CUDA(cudaMemsetAsync(loss, 0, sizeof(float), stream));
+  HEXA_CUDA(cudaMemsetAsync(workspace, 0, 16, stream));
+  if (num_tokens == 0) return HEXA_OK;
+  unsigned int* ticket = static_cast<unsigned int*>(workspace);
+  float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kGateTicketBytes);
+  int grid = gate_grid(num_tokens);
+  if (grid > kGateMaxBlocks / 2) grid = kGateMaxBlocks / 2;      // two partial rows per block
+  const float inv_sigma = 1.f / sigma;
+#define HEXA_GATE_LI(V)                                                                                                     \
+  gate_topk_li_kernel<V><<<grid, kGateThreads, 0, stream>>>(logits, logits_w_noise, ld, num_tokens, num_experts, top_k, inv_sigma, \
+                                                            ids, importance, load, loss, ticket, partial)
+  const int vpt = (num_experts + 31) / 32;
+  if (vpt <= 1) HEXA_GATE_LI(1);
+  else if (vpt <= 2) HEXA_GATE_LI(2);
+  else if (vpt <= 4) HEXA_GATE_LI(4);
+  else if (vpt <= 8) HEXA_GATE_LI(8);
+  else HEXA_GATE_LI(16);
+#undef HEXA_GATE_LI
+  HEXA_LAUNCH_CHECK("gate_topk_li_kernel");
+  return HEXA_OK;
+}
+
+extern "C" int hexa_gate_load_importance_grad(const float* logits, const float* logits_w_noise, int64_t ld, int64_t num_tokens,
+                                              int num_experts, int top_k, float sigma, const float* importance, const float* load,
+                                              const float* dloss, float* dlogits, int64_t ldd, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  HEXA_REQUIRE(num_tokens >= 0 && num_experts >= 1 && num_experts <= kGateMaxExperts,
+               "hexa_gate_load_importance_grad: needs 1 <= experts <= %d (got %d)", kGateMaxExperts, num_experts);
+  HEXA_REQUIRE(top_k >= 1 && top_k <= num_experts && sigma > 0.f, "hexa_gate_load_importance_grad: bad top_k or sigma");
+  if (num_tokens == 0) return HEXA_OK;
+  HEXA_REQUIRE(logits && logits_w_noise && importance && load && dloss && dlogits && ld >= num_experts && ldd >= num_experts,
+               "hexa_gate_load_importance_grad: null pointer or leading dimension < experts");
+  const int grid = gate_grid(num_tokens);
+  const float inv_sigma = 1.f / sigma;
+#define HEXA_GATE_LIG(V)                                                                                                     \
+  gate_li_grad_kernel<V><<<grid, kGateThreads, 0, stream>>>(logits, logits_w_noise, ld, num_tokens, num_experts, top_k, inv_sigma, \
+                                                            importance, load, dloss, dlogits, ldd)
+  const int vpt = (num_experts + 31) / 32;
+  if (vpt <= 1) HEXA_GATE_LIG(1);
+  else if (vpt <= 2) HEXA_GATE_LIG(2);
+  else if (vpt <= 4) HEXA_GATE_LIG(4);
+  else if (vpt <= 8) HEXA_GATE_LIG(8);
+  else HEXA_GATE_LIG(16);
+#undef HEXA_GATE_LIG
+  HEXA_LAUNCH_CHECK("gate_li_grad_kernel");
   return HEXA_OK;
 }

@@ -35,7 +35,7 @@ from torch.nn import ModuleList, Parameter, ParameterList
 from .. import _lib as L
 from . import losses
 from .activations import classify
-from .gating import GATES, fused_topk_gshard
+from .gating import GATES, fused_topk_gshard, fused_topk_load_importance
 from .layers import FusedMoE_Shared_CudaCore, MLP_Implement, simplified_extract_critical
 from .param_cache import DenseGradReducer, PipelineSharedCache
 
@@ -333,6 +333,11 @@ class MoE_Cascaded(torch.nn.Module):
             logits_w_noise = logits
         if self.is_gshard_loss:
             fused = fused_topk_gshard(logits_w_noise, top_k, getattr(self.dispatch_params, "backend", None))
+            if fused is not None:
+                return fused
+        elif logits_w_noise is not logits:
+            fused = fused_topk_load_importance(logits, logits_w_noise, top_k, gate.gate_noise,
+                                               getattr(self.dispatch_params, "backend", None))
             if fused is not None:
                 return fused
         scores = F.softmax(logits_w_noise, dim=1)

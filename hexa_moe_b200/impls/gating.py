@@ -141,4 +141,44 @@ def fused_topk_gshard(logits, top_k, backend):
     return list(ids.unbind(0)), l_aux
 
 
+class _TopKWithLoadImportanceLoss(torch.autograd.Function):
+    """(ids int32 [k,T], l_aux) from the clean and the noisy float32 logits [T,E]: top-k of the noisy logits and the
+    load-importance loss of the clean ones in one kernel, its gradient in another.  Same values as the reference chain
+    F.softmax(noisy) -> torch.topk, load_importance_loss(F.softmax(clean), noisy.gather(ids), E, gate_noise)
+    (cascaded_moe.py:568-598, losses.py:21-43) up to summation order."""
+
+    @staticmethod
+    def forward(ctx, logits, logits_w_noise, top_k, sigma, backend):
+        ids, loss, importance, load = backend.gate_topk_load_importance(logits, logits_w_noise, top_k, sigma)
+        ctx.backend, ctx.top_k, ctx.sigma = backend, top_k, sigma
+        ctx.save_for_backward(logits, logits_w_noise, importance, load)
+        ctx.mark_non_differentiable(ids)
+        return ids, loss
+
+    @staticmethod
+    def backward(ctx, _d_ids, d_loss):
+        if d_loss is None:
+            return None, None, None, None, None
+        logits, noisy, importance, load = ctx.saved_tensors
+        g = ctx.backend.gate_load_importance_grad(logits, noisy, ctx.top_k, ctx.sigma, importance, load, d_loss)
+        # the loss depends on the clean logits through softmax and on the noisy ones through the threshold; the noisy
+        # logits are the clean ones plus a constant, so the kernel returns the sum and the noisy input gets none
+        return g, None, None, None, None
+
+
+def fused_topk_load_importance(logits, logits_w_noise, top_k, gate_noise, backend):
+    """The fused path of the load-importance loss when it applies (float32 CUDA logits, noise > 0, expert count within
+    the kernel's limit), else None."""
+    if (backend is None or not hasattr(backend, "gate_topk_load_importance") or not logits.is_cuda
+            or logits.dtype != torch.float32 or logits_w_noise.dtype != torch.float32 or logits.dim() != 2
+            or logits_w_noise is logits or gate_noise <= 0 or os.environ.get("HEXA_FUSED_GATE", "1") == "0"):
+        return None
+    E = logits.shape[1]
+    if E > backend.gate_max_experts() or logits.shape[0] == 0:
+        return None
+    ids, l_aux = _TopKWithLoadImportanceLoss.apply(logits.contiguous(), logits_w_noise.detach().contiguous(), min(int(top_k), E),
+                                                   float(gate_noise) / E, backend)
+    return list(ids.unbind(0)), l_aux
+
+
 GATES = {"top": LinearTopKGate, "cosine_top": CosineTopKGate}

@@ -299,6 +299,41 @@ def gate_loss_grad(logits: torch.Tensor, first_count: torch.Tensor, dloss: torch
     return out
 
 
+def gate_topk_load_importance(logits: torch.Tensor, logits_w_noise: torch.Tensor, top_k: int, sigma: float):
+    """top-k of the noisy logits + the load-importance loss of the clean ones in one kernel.  Returns (ids int32 [k,T]
+    route-major, loss float32 scalar tensor, importance float32 [E], load float32 [E])."""
+    for t in (logits, logits_w_noise):
+        if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise L.HexaError("gate_topk_load_importance: logits must be float32 [T,E] with unit inner stride")
+    if logits.shape != logits_w_noise.shape or logits.stride(0) != logits_w_noise.stride(0):
+        raise L.HexaError("gate_topk_load_importance: the two logit tensors must have the same shape and row pitch")
+    T, E = logits.shape
+    dev = logits.device
+    ids = torch.empty(top_k, T, dtype=torch.int32, device=dev)
+    imp = torch.empty(E, dtype=torch.float32, device=dev)
+    load = torch.empty(E, dtype=torch.float32, device=dev)
+    loss = torch.empty((), dtype=torch.float32, device=dev)
+    ws = torch.empty(int(lib().hexa_gate_workspace_bytes()), dtype=torch.uint8, device=dev)
+    with _Timed("gate", 3.0 * T * E * 4):
+        check(lib().hexa_gate_topk_load_importance(ptr(logits), ptr(logits_w_noise), _ld(logits), T, E, top_k, float(sigma), ptr(ids),
+                                                   ptr(imp), ptr(load), ptr(loss), ptr(ws), ws.numel(), stream_of(logits)),
+              "hexa_gate_topk_load_importance")
+    return ids, loss, imp, load
+
+
+def gate_load_importance_grad(logits, logits_w_noise, top_k: int, sigma: float, importance, load, dloss) -> torch.Tensor:
+    """Gradient of gate_topk_load_importance's loss with respect to the clean logits, scaled by the device scalar dloss
+    (the noisy logits differ from them by a constant, so this is also the whole gradient through the threshold)."""
+    T, E = logits.shape
+    out = torch.empty(T, E, dtype=torch.float32, device=logits.device)
+    dloss = dloss.detach().to(torch.float32).reshape(1).contiguous()
+    with _Timed("gate", 3.0 * T * E * 4):
+        check(lib().hexa_gate_load_importance_grad(ptr(logits), ptr(logits_w_noise), _ld(logits), T, E, top_k, float(sigma),
+                                                   ptr(importance), ptr(load), ptr(dloss), ptr(out), _ld(out), stream_of(logits)),
+              "hexa_gate_load_importance_grad")
+    return out
+
+
 # -------------------------------------------------------------------------------------------------
 # one MoE layer on one device
 # -------------------------------------------------------------------------------------------------

@@ -278,6 +278,22 @@ int hexa_gate_topk(const float* logits, int64_t ld, int64_t num_tokens, int num_
 int hexa_gate_loss_grad(const float* logits, int64_t ld, int64_t num_tokens, int num_experts, const int32_t* first_count,
                         const float* dloss, float* dlogits, int64_t ldd, void* stream);
 
+/* The same step for the other auxiliary loss of the reference, the load-importance loss (impls/losses.py:21-43, selected by
+ * is_gshard_loss=False; needs gate noise): ids = top-k of the NOISY logits (what torch.topk of softmax(noisy) returns),
+ *   importance[e] = sum_t softmax(logits)[t,e],   load[e] = sum_t Phi((softmax(logits)[t,e] - thr_t) / sigma),
+ *   thr_t = k-th largest noisy logit of token t, sigma = gate_noise / num_experts,
+ *   loss = (cv2(importance) + cv2(load)) / 2 with cv2(v) = var_unbiased(v) / (mean(v)^2 + 1e-10)
+ * (the reference compares a score with a logit in `load`; kept as it is).  logits and logits_w_noise are float32
+ * [num_tokens, num_experts] with the same leading dimension; sums in fixed order (bit-identical from run to run);
+ * workspace as for hexa_gate_topk.  The gradient entry point recomputes softmax, top-k and the normal density from the two
+ * logit tensors and the forward's importance / load totals; dloss is a float in device memory. */
+int hexa_gate_topk_load_importance(const float* logits, const float* logits_w_noise, int64_t ld, int64_t num_tokens,
+                                   int num_experts, int top_k, float sigma, int32_t* ids, float* importance, float* load,
+                                   float* loss, void* workspace, size_t workspace_bytes, void* stream);
+int hexa_gate_load_importance_grad(const float* logits, const float* logits_w_noise, int64_t ld, int64_t num_tokens,
+                                   int num_experts, int top_k, float sigma, const float* importance, const float* load,
+                                   const float* dloss, float* dlogits, int64_t ldd, void* stream);
+
 /* Elementwise helper on sorted rows for activations the epilogue does not know:
  * dst[r,:] = row_token[r] >= 0 ? src[r,:] : 0 (restores the zero-pad-row invariant). */
 int hexa_mask_pad_rows(void* buf, int64_t ld, const int32_t* row_token, const int32_t* pad_offsets,

@@ -245,6 +245,19 @@ def gshard_loss(scores: torch.Tensor, top_ids: torch.Tensor) -> torch.Tensor:
     return (scores.sum(0) * ce).sum() / T
 
 
+def load_importance_loss(scores_wo_noise: torch.Tensor, topk_logits: torch.Tensor, num_experts: int, gate_noise: float):
+    """impls/losses.py:21-43: mean of the squared coefficients of variation of importance (column sums of the clean
+    softmax) and load (column sums of Phi((clean score - k-th largest noisy logit) / (gate_noise / E))); unbiased
+    variance, 1e-10 added to the squared mean.  Evaluated in the dtype of its inputs (the tests pass float64)."""
+    sigma = gate_noise / num_experts
+    threshold = topk_logits[:, -1].reshape(-1, 1)
+    z = (scores_wo_noise - threshold) / sigma
+    load = (0.5 * (1.0 + torch.erf(z / math.sqrt(2.0)))).sum(0)
+    importance = scores_wo_noise.sum(0)
+    cv2 = lambda v: v.var() / (v.mean() ** 2 + 1e-10)
+    return (cv2(importance) + cv2(load)) / 2.0
+
+
 def gate_topk(x, wg, top_k, noise: Optional[torch.Tensor] = None, gate_noise: float = 0.0):
     """logits = x @ wg^T (gates/top.py:20-22); optional noise * gate_noise / E
     (impls/cascaded_moe.py:571-572); softmax; top-k indices (impls/layers.py:483); gshard loss."""

@@ -107,3 +107,76 @@ def test_module_routes_through_the_fused_gate_and_matches_the_pytorch_chain():
     assert abs(fused[1] - plain[1]) <= 1e-5 * abs(plain[1])
     for a, b in ((fused[0], plain[0]), (fused[2], plain[2]), (fused[3], plain[3])):
         assert float((a - b).abs().max()) <= 2e-2 * float(b.abs().max())
+
+
+@pytest.mark.parametrize("T,E,k", [(1000, 64, 2), (257, 7, 1), (4096, 8, 4), (33, 300, 3), (70000, 32, 2)])
+def test_load_importance_ids_loss_and_gradient_match_the_oracle(T, E, k):
+    """The other auxiliary loss of the reference (is_gshard_loss=False, impls/losses.py:21-43): ids of the noisy logits
+    bit-exact, loss and its gradient against float64 autograd of the oracle's restatement (1e-5 of their scale), and
+    bit-identical outputs from run to run."""
+    from hexa_moe_b200 import ops
+    g = torch.Generator().manual_seed(T + E)
+    logits = torch.randn(T, E, generator=g) * 0.05
+    gate_noise = 1.0
+    noisy = logits + gate_noise * torch.randn(T, E, generator=g) / E
+    ids, loss, importance, load = ops.gate_topk_load_importance(logits.cuda(), noisy.cuda(), k, gate_noise / E)
+    want_ids = torch.topk(F.softmax(noisy, dim=1), k, dim=1).indices
+    got = ids.cpu().t().long()
+    same = got == want_ids
+    if not bool(same.all()):           # two noisy logits within an ulp of each other may swap
+        assert float(same.float().mean()) > 0.999
+    ref = logits.double().requires_grad_(True)
+    noisy_ref = ref + (noisy.double() - logits.double())
+    want = O.load_importance_loss(F.softmax(ref, dim=1), noisy_ref.gather(1, got), E, gate_noise)
+    assert abs(float(loss) - float(want)) <= 1e-5 * abs(float(want)), (float(loss), float(want))
+    assert torch.allclose(importance.cpu().double(), F.softmax(ref, dim=1).sum(0).detach(), rtol=1e-5, atol=1e-6)
+    (want * 3.0).backward()
+    grad = ops.gate_load_importance_grad(logits.cuda(), noisy.cuda(), k, gate_noise / E, importance, load,
+                                         torch.tensor(3.0, device="cuda"))
+    scale = float(ref.grad.abs().max())
+    # fp32 kernel against float64: the gradient factors of var / mean^2 are differences of nearly equal column sums
+    assert float((grad.cpu().double() - ref.grad).abs().max()) <= 2e-3 * scale
+    again = ops.gate_topk_load_importance(logits.cuda(), noisy.cuda(), k, gate_noise / E)
+    for a, b in zip((ids, loss, importance, load), again):
+        assert torch.equal(a, b)
+
+
+def test_module_with_the_load_importance_loss_takes_the_fused_gate():
+    """is_gshard_loss=False in training mode: the fused kernels and the PyTorch chain (HEXA_FUSED_GATE=0) see the same
+    noise (same seed) and give the same output, auxiliary loss and gradients."""
+    import os
+    from hexa_moe import moe as hmoe
+    from hexa_moe_b200 import ops
+    torch.manual_seed(12)
+    m = hmoe.MoE_Cascaded(gate_type={'type': 'top', 'k': 2, 'fp32_gate': True, 'gate_noise': 1.0}, model_dim_list=[64],
+                          moe_idx_list=[0], mlp_ratio=4, num_global_experts=8, total_depth=1, data_centric=True,
+                          is_gshard_loss=False, activation_fn=lambda t: F.gelu(t))
+    with torch.no_grad():
+        for n_, p in m.named_parameters():
+            p.normal_(0, 0.02 if "gates" in n_ else 0.1)
+    m = m.to(torch.bfloat16).cuda().train()
+    x = torch.randn(300, 64, device="cuda").bfloat16()
+
+    def run():
+        torch.manual_seed(99)                        # the same noise draw both times
+        xi = x.clone().requires_grad_(True)
+        y, aux = m(0, xi)
+        (y.float().sum() + 5.0 * aux).backward()
+        return y.detach().float(), float(aux), xi.grad.float(), m.gates[0].wg.weight.grad.clone()
+
+    m.zero_grad()
+    before = ops.LAUNCHES
+    fused = run()
+    n_fused = ops.LAUNCHES - before
+    os.environ["HEXA_FUSED_GATE"] = "0"
+    try:
+        m.zero_grad()
+        before = ops.LAUNCHES
+        plain = run()
+        n_plain = ops.LAUNCHES - before
+    finally:
+        del os.environ["HEXA_FUSED_GATE"]
+    assert n_fused == n_plain + 2                                # one gate kernel each way
+    assert abs(fused[1] - plain[1]) <= 1e-4 * abs(plain[1])
+    for a, b in ((fused[0], plain[0]), (fused[2], plain[2]), (fused[3], plain[3])):
+        assert float((a - b).abs().max()) <= 2e-2 * float(b.abs().max())

@@ -243,3 +243,22 @@ print("DEADLOCK" if t.is_alive() else out[0])
 ''' % ROOT
     res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=180)
     assert "DEADLOCK" not in res.stdout and ("installed" in res.stdout or "entry point reached" in res.stdout), res.stdout + res.stderr
+
+
+def test_load_importance_loss_of_the_module_equals_the_oracle_restatement():
+    """impls/losses.py:load_importance_loss (what the PyTorch-op path of the module evaluates, reference
+    hexa_moe/impls/losses.py:21-43) against the oracle's float64 restatement, value and gradient."""
+    from hexa_moe_b200.impls import losses
+    from oracle import hexa_oracle as O
+    g = torch.Generator().manual_seed(4)
+    T, E, k, noise = 500, 16, 2, 1.0
+    logits = (torch.randn(T, E, generator=g) * 0.05).requires_grad_(True)
+    noisy = logits + noise * torch.randn(T, E, generator=g) / E
+    ids = torch.topk(F.softmax(noisy, dim=1), k, dim=1).indices
+    got = losses.load_importance_loss(F.softmax(logits, dim=1), noisy.gather(1, ids), E, noise)
+    ref = logits.detach().double().requires_grad_(True)
+    noisy_ref = ref + (noisy.detach().double() - logits.detach().double())
+    want = O.load_importance_loss(F.softmax(ref, dim=1), noisy_ref.gather(1, ids), E, noise)
+    assert abs(float(got) - float(want)) <= 1e-5 * abs(float(want))
+    got.backward(); want.backward()
+    assert float((logits.grad.double() - ref.grad).abs().max()) <= 2e-3 * float(ref.grad.abs().max())      # fp32 chain vs float64
