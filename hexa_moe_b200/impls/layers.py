@@ -177,7 +177,7 @@ def _dense_on_kernels(cfg, x: Tensor) -> bool:
     return (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and getattr(cfg, "act_id", -1) >= 0
             and getattr(cfg, "backend", None) is not None and hasattr(cfg.backend, "dense_forward")
             and x.shape[0] > 0 and x.shape[1] % 8 == 0
-            and x.shape[1] >= int(os.environ.get("HEXA_DENSE_MIN_DIM", "512")))
+            and x.shape[1] >= int(os.environ.get("HEXA_DENSE_MIN_DIM", "256")))
 
 
 class MLP_Implement(torch.autograd.Function):

@@ -211,7 +211,7 @@ def test_dense_ffn_on_the_grouped_gemm_kernels(dtype, tokens):
         return [y.detach(), xi.grad] + [params[n_].grad.clone() for n_ in names]
 
     from hexa_moe_b200 import ops
-    os.environ["HEXA_DENSE_MIN_DIM"] = "0"          # by default only model dims >= 512 take the kernel path
+    os.environ["HEXA_DENSE_MIN_DIM"] = "0"          # by default only model dims >= 256 take the kernel path
     try:
         before = ops.LAUNCHES
         got = run()
