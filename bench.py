@@ -199,6 +199,25 @@ def cpu_sample_text(k, E):
             f"per-token work as the full layer, fp32, all host cores")
 
 
+def layer_config(args, d, H, E, k, L, T, proportion):
+    """The `config` object of the layer workloads: the same for this library's arm and for the reference arm."""
+    return dict(workload=args.workload + "-layer", d_model=d, hidden=H, experts=E, hidden_split=proportion, top_k=k, layers=L,
+                tokens_per_gpu=T, activation="gelu", mode=args.mode + "-centric",
+                l2="inputs larger than L2 (expert weights %.1f GB per layer)" % (2 * E * H * d * 2 / 1e9))
+
+
+def hetero_proportion(args, world):
+    """(mode, hidden split, tokens per rank) of the heterogeneous model-centric case, else the arguments' own."""
+    if not args.hetero:
+        return None, None
+    if 8 % world:
+        raise SystemExit("--hetero needs 1, 2, 4 or 8 ranks")
+    args.mode = "model"
+    eighth = [0.2, 0.2, 0.15, 0.15, 0.1, 0.1, 0.05, 0.05]
+    g = 8 // world
+    return [round(sum(eighth[i * g:(i + 1) * g]), 6) for i in range(world)], world
+
+
 def run_reference(args):
     """The reference has no CPU implementation of this path (its kernels are Triton / CUDA only), so this arm
     times the CPU oracle port of the same layer on the host cores, on a bounded token sample per step."""
@@ -209,8 +228,11 @@ def run_reference(args):
         print(json.dumps(dict(impl="reference", unavailable="no CPU arm for workload %s: use one of %s"
                                                             % (args.workload, ", ".join(WORKLOADS)))), flush=True)
         return
-    d, H, EXPERTS, _ = WORKLOADS[args.workload]
+    d, H, EXPERTS, T_default = WORKLOADS[args.workload]
     k = TOP_K
+    world = max(int(args.gpus), 1)
+    proportion, _ = hetero_proportion(args, world)
+    T = (args.tokens or T_default) // (world if args.hetero else 1)
     n = CPU_SAMPLE_TOKENS
     data = cpu_sample(d, H, k)
     for _ in range(min(args.warmup, 1)):
@@ -222,9 +244,10 @@ def run_reference(args):
     line = dict(metric="moe_layer_fwd_bwd_tokens_per_s", value=val, unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
                 warmup=args.warmup, ms_per_step=dt * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None,
                 dtype="f32", data="synthetic", impl="reference",
-                config=dict(workload=args.workload + "-layer", d_model=d, hidden=H, experts=EXPERTS,
-                            top_k=k, note="CPU oracle port: the reference ships no CPU path for these operators"),
-                cpu_baseline=dict(value=val, unit="tokens/s", cores=cores, kind="port", sample=sample, extrapolated=False),
+                config=layer_config(args, d, H, EXPERTS, k, LAYERS, T, proportion),
+                cpu_baseline=dict(value=val, unit="tokens/s", cores=cores, kind="port", sample=sample, extrapolated=False,
+                                  note="CPU oracle port of the layer (fp32 grouped matmuls per expert): the reference ships "
+                                       "no CPU path for these operators; one layer, one rank's host cores"),
                 e2e=dict(value=val, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
 
@@ -586,14 +609,8 @@ def main():
     d, H, E, T_default = WORKLOADS[args.workload]
     k, L = TOP_K, LAYERS
     T = args.tokens or T_default
-    proportion = None
+    proportion, _ = hetero_proportion(args, world)
     if args.hetero:
-        if 8 % world:
-            raise SystemExit("--hetero needs 1, 2, 4 or 8 ranks")
-        args.mode = "model"
-        eighth = [0.2, 0.2, 0.15, 0.15, 0.1, 0.1, 0.05, 0.05]
-        g = 8 // world
-        proportion = [round(sum(eighth[i * g:(i + 1) * g]), 6) for i in range(world)]
         T = (args.tokens or T_default) // world            # the token count is global: every rank contributes its share
     torch.manual_seed(0)
     m = hmoe.MoE_Cascaded(gate_type={'type': 'top', 'k': k, 'fp32_gate': True}, model_dim_list=[d] * L,
@@ -739,9 +756,7 @@ def main():
         line = dict(metric="moe_layer_fwd_bwd_tokens_per_s", value=value, unit="tokens/s", n_gpus=n_gpus, steps=args.steps,
                     warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True,
                     scaling="strong" if args.hetero else "weak", vs_baseline=None, dtype="bf16", data="synthetic",
-                    config=dict(workload=args.workload + "-layer", d_model=d, hidden=H, experts=E, hidden_split=proportion,
-                                top_k=k, layers=L, tokens_per_gpu=T, activation="gelu", mode=args.mode + "-centric",
-                                l2="inputs larger than L2 (expert weights %.1f GB per layer)" % (2 * E * H * d * 2 / 1e9)),
+                    config=layer_config(args, d, H, E, k, L, T, proportion),
                     model_tflops_per_gpu=layer_flops / (ms * 1e-3) / 1e12,
                     model_frac_of_burst=layer_flops / (ms * 1e-3) / 1e12 / pk["burst"],
                     e2e=dict(value=e2e_value, unit="tokens/s", ms_per_step=ms_e2e, h2d_bytes_per_step=x_host.numel() * 2,

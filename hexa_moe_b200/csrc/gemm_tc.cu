@@ -911,7 +911,8 @@ int env_int(const char* name, int dflt) {
 int epi_warps_for(int64_t num_kb_typical) {
   const int forced = env_int("HEXA_TC_EPI_WARPS", 0);
   if (forced == 4 || forced == 8 || forced == 16) return forced;
-  const int64_t threshold = env_int("HEXA_TC_EPI_WARPS_KB", 0);     // 0: always 16 (the measured default, see DESIGN)
+  const int64_t threshold = env_int("HEXA_TC_EPI_WARPS_KB", 0);     // 0: always 16 (the faster setting at K = 768 and, for the
+                                                                     // launches with an activation, at K = 2048 as well)
   return (threshold > 0 && num_kb_typical >= threshold) ? 8 : 16;
 }
 
