@@ -262,3 +262,21 @@ def test_load_importance_loss_of_the_module_equals_the_oracle_restatement():
     assert abs(float(got) - float(want)) <= 1e-5 * abs(float(want))
     got.backward(); want.backward()
     assert float((logits.grad.double() - ref.grad).abs().max()) <= 2e-3 * float(ref.grad.abs().max())      # fp32 chain vs float64
+
+
+def test_bench_arms_describe_the_same_configuration():
+    """bench.py prints the same `config` object for this library's arm and for the reference arm, and the heterogeneous
+    split of config 5 merges neighbouring shares for fewer than eight ranks."""
+    import argparse
+    import bench
+    for world, want in ((8, [0.2, 0.2, 0.15, 0.15, 0.1, 0.1, 0.05, 0.05]), (4, [0.4, 0.3, 0.2, 0.1]), (2, [0.7, 0.3]), (1, [1.0])):
+        args = argparse.Namespace(hetero=True, mode="data", workload="c5", tokens=0, gpus=world)
+        split, _ = bench.hetero_proportion(args, world)
+        assert split == want and abs(sum(split) - 1) < 1e-9 and args.mode == "model"
+        cfg = bench.layer_config(args, 2048, 8192, 64, 2, 2, 131072 // world, split)
+        assert cfg["mode"] == "model-centric" and cfg["hidden_split"] == want and cfg["tokens_per_gpu"] == 131072 // world
+    args = argparse.Namespace(hetero=False, mode="data", workload="c5", tokens=0, gpus=1)
+    assert bench.hetero_proportion(args, 1) == (None, None) and args.mode == "data"
+    assert bench.cpu_sample_text(2, 64).startswith("16384 tokens (seed 0) top-2 over 8 of the 64 experts")
+    assert set(bench.TRAFFIC_RATIO) == {"esmm:fc1_forward_act", "esmm:fc2_forward", "estmm:dw2", "esmm:fc2_dgrad_dact",
+                                        "estmm:dw1", "esmm:fc1_dgrad"}
