@@ -406,11 +406,12 @@ __device__ __forceinline__ void stage_row(uint8_t* buf, int r, const uint32_t (&
 }
 
 // Values of 16 columns of one row for the two possible outputs of the ESMM epilogue: y = acc + bias packed as it
-// is (the saved pre-activation), o = the layer output of this GEMM.  Rows that are padding produce zeros.  Working on
-// 16 columns at a time keeps few enough values live for the compiler to interleave the independent activations.
+// is (the saved pre-activation), o = the layer output of this GEMM.  Rows that are padding come out as zeros without a
+// select per element: their accumulator is exactly zero (the A operand's pad rows are zeros), the caller has masked
+// their bias, and every activation here maps 0 to 0 (the derivative epilogue multiplies the zero accumulator).  Working
+// on 16 columns at a time keeps few enough values live for the compiler to interleave the independent activations.
 template <int EPI, int ACT, int is_bf16>
-__device__ __forceinline__ void epi_values16(const float (&f)[16], const uint16_t* xp, bool live, int ncols,
-                                             uint32_t* y, uint32_t* o) {
+__device__ __forceinline__ void epi_values16(const float (&f)[16], const uint16_t* xp, int ncols, uint32_t* y, uint32_t* o) {
   if (EPI == HEXA_EPI_DACT) {
 #pragma unroll
     for (int g = 0; g < 2; ++g) {
@@ -419,18 +420,17 @@ __device__ __forceinline__ void epi_values16(const float (&f)[16], const uint16_
       const uint32_t* ap = reinterpret_cast<const uint32_t*>(&a);
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        o[4 * g + i] = live ? pack2(f[8 * g + 2 * i] * act_grad_fast<ACT>(unpack_lo(ap[i], is_bf16)),
-                                    f[8 * g + 2 * i + 1] * act_grad_fast<ACT>(unpack_hi(ap[i], is_bf16)), is_bf16)
-                            : 0u;
+        o[4 * g + i] = pack2(f[8 * g + 2 * i] * act_grad_fast<ACT>(unpack_lo(ap[i], is_bf16)),
+                             f[8 * g + 2 * i + 1] * act_grad_fast<ACT>(unpack_hi(ap[i], is_bf16)), is_bf16);
     }
   } else {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       if (EPI == HEXA_EPI_ACT) {
-        y[i] = live ? pack2(f[2 * i], f[2 * i + 1], is_bf16) : 0u;
-        o[i] = live ? pack2(act_fast<ACT>(f[2 * i]), act_fast<ACT>(f[2 * i + 1]), is_bf16) : 0u;
+        y[i] = pack2(f[2 * i], f[2 * i + 1], is_bf16);
+        o[i] = pack2(act_fast<ACT>(f[2 * i]), act_fast<ACT>(f[2 * i + 1]), is_bf16);
       } else {
-        o[i] = live ? pack2(f[2 * i], f[2 * i + 1], is_bf16) : 0u;
+        o[i] = pack2(f[2 * i], f[2 * i + 1], is_bf16);
       }
     }
   }
@@ -700,6 +700,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         } else {
           const int64_t r = (int64_t)tile.row0 + rloc;
+          // a pad row skips the bias, which is the only thing that could make it non-zero
           const bool live = p.row_token == nullptr || p.row_token[r] >= 0;
           uint32_t yv[16], ov[16];
 #pragma unroll
@@ -711,7 +712,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             float f[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
-            if (p.bias && ncols > 0) {
+            if (p.bias && ncols > 0 && live) {
               const float* bp = p.bias + (int64_t)tile.e * p.ldbias + hcol;
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
@@ -727,8 +728,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // one specialisation per (epilogue, activation, 16-bit flavour): no per-element branches
 #define HEXA_EPI_CASE(E_, A_)                                                                          \
   case E_ * 8 + A_:                                                                                    \
-    if (is_bf16) epi_values16<E_, A_, 1>(f, xp, live, ncols, yh, oh);                                  \
-    else epi_values16<E_, A_, 0>(f, xp, live, ncols, yh, oh);                                          \
+    if (is_bf16) epi_values16<E_, A_, 1>(f, xp, ncols, yh, oh);                                        \
+    else epi_values16<E_, A_, 0>(f, xp, ncols, yh, oh);                                                \
     break;
             switch ((p.debug & 8) ? 99 : p.epilogue * 8 + p.act) {
               HEXA_EPI_CASE(HEXA_EPI_ACT, HEXA_ACT_RELU)
@@ -741,8 +742,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               HEXA_EPI_CASE(HEXA_EPI_DACT, HEXA_ACT_GELU_TANH)
               HEXA_EPI_CASE(HEXA_EPI_DACT, HEXA_ACT_SILU)
               default:
-                if (is_bf16) epi_values16<HEXA_EPI_LINEAR, HEXA_ACT_NONE, 1>(f, xp, live, ncols, yh, oh);
-                else epi_values16<HEXA_EPI_LINEAR, HEXA_ACT_NONE, 0>(f, xp, live, ncols, yh, oh);
+                if (is_bf16) epi_values16<HEXA_EPI_LINEAR, HEXA_ACT_NONE, 1>(f, xp, ncols, yh, oh);
+                else epi_values16<HEXA_EPI_LINEAR, HEXA_ACT_NONE, 0>(f, xp, ncols, yh, oh);
                 break;
             }
 #undef HEXA_EPI_CASE
