@@ -66,6 +66,9 @@ struct Params {
   int64_t k;        // ESMM: contraction length ; ESTMM: unused
   int64_t m;        // ESTMM: output rows per expert
   int E;
+  uint32_t nt;          // tile columns of the output: ceil(n / BN)
+  uint32_t per_expert;  // ESTMM: tiles per expert = tile rows x tile columns x splits
+  uint32_t total_tiles; // ESTMM: E x per_expert ; ESMM single-CTA: unused (the row count is device-side)
   int e_begin, e_end;   // ESMM: only tiles of experts in [e_begin, e_end) are computed by this launch
   int epilogue, act;
   int is_bf16;      // 16-bit flavour of the inputs (and of 16-bit outputs)
@@ -331,49 +334,52 @@ struct Tile {
 };
 
 // Tile t of the static list, as seen by CTA `rank` of its pair (rank = 0 when CTAS = 1).  Returns false past the end.
+// The tile index and every quantity it is divided by are 32-bit (the host checks the tile count): the lookup runs once
+// per tile in each of the three roles, two of which are single threads that the tensor pipe waits for, and a 64-bit
+// division is a ~100-instruction sequence.
 template <int BN, int MODE, int CTAS>
-__device__ __forceinline__ bool get_tile(const Params& p, int64_t t, int rank, Tile& tile) {
+__device__ __forceinline__ bool get_tile(const Params& p, uint32_t t, int rank, Tile& tile) {
   if (MODE == ESTMM) {
-    const int64_t MT = (p.m + BLOCK_M * CTAS - 1) / (BLOCK_M * CTAS), NT = (p.n + BN - 1) / BN;
-    const int64_t S = p.splits;
-    if (t >= (int64_t)p.E * MT * NT * S) return false;
-    const int e = (int)(t / (MT * NT * S));
-    const int64_t rem = (t - (int64_t)e * MT * NT * S) / S;
-    const int c = (int)(t % S);
-    tile.e = e;
-    tile.m0 = ((int)(rem / NT) * CTAS + rank) * BLOCK_M;
-    tile.col0 = (int)(rem % NT) * BN;
+    if (t >= p.total_tiles) return false;
+    const uint32_t S = (uint32_t)p.splits;
+    const uint32_t e = t / p.per_expert;
+    const uint32_t in_e = t - e * p.per_expert;
+    const uint32_t rem = in_e / S;
+    const uint32_t c = in_e - rem * S;
+    const uint32_t mrow = rem / p.nt;
+    tile.e = (int)e;
+    tile.m0 = ((int)mrow * CTAS + rank) * BLOCK_M;
+    tile.col0 = (int)(rem - mrow * p.nt) * BN;
     const int seg0 = p.pad_offsets[e];
     const int kb_all = (p.pad_offsets[e + 1] - seg0) / BLOCK_K;
-    const int kb_per = (int)((kb_all + S - 1) / S);          // chunks of equal length, the last ones may be short or empty
-    const int kb0 = c * kb_per;
+    const int kb_per = (kb_all + (int)S - 1) / (int)S;       // chunks of equal length, the last ones may be short or empty
+    const int kb0 = (int)c * kb_per;
     tile.row0 = seg0 + kb0 * BLOCK_K;
     tile.num_kb = max(0, min(kb_per, kb_all - kb0));
-    tile.split = c;
+    tile.split = (int)c;
     tile.skip = 0;
     tile.valid = tile.m0 < p.m;
     return true;
   } else {
-    const int64_t NT = (p.n + BN - 1) / BN;
-    int64_t mb;
+    const uint32_t row_tile = t / p.nt;          // pair index (CTAS = 2) or 128-row block
+    uint32_t mb;
     if (CTAS == 2) {
-      const int64_t pr = t / NT;
-      if (pr >= p.max_pairs) return false;
-      const int pb = p.pair_block[pr];
+      if (row_tile >= (uint32_t)p.max_pairs) return false;
+      const int pb = p.pair_block[row_tile];
       if (pb < 0) return false;
-      mb = (pb >> 1);
+      mb = (uint32_t)(pb >> 1);
       tile.e = p.tile_expert[mb];
       tile.valid = rank == 0 || (pb & 1);
-      mb += rank;
+      mb += (uint32_t)rank;
     } else {
-      const int64_t mblocks = p.pad_offsets[p.E] / BLOCK_M;
-      if (t >= mblocks * NT) return false;
-      mb = t / NT;
+      const uint32_t mblocks = (uint32_t)(p.pad_offsets[p.E] / BLOCK_M);
+      if (row_tile >= mblocks) return false;
+      mb = row_tile;
       tile.e = p.tile_expert[mb];
       tile.valid = 1;
     }
     tile.row0 = (int)(mb * BLOCK_M);
-    tile.col0 = (int)(t % NT) * BN;
+    tile.col0 = (int)(t - row_tile * p.nt) * BN;
     tile.m0 = 0;
     tile.num_kb = (int)((p.k + BLOCK_K - 1) / BLOCK_K);
     tile.skip = tile.e < p.e_begin || tile.e >= p.e_end;
@@ -462,8 +468,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = CTAS == 2 ? (int)cluster_ctarank() : 0;    // 0 = leader of the pair
-  const int64_t tile_first = CTAS == 2 ? (blockIdx.x >> 1) : blockIdx.x;
-  const int64_t tile_step = CTAS == 2 ? (gridDim.x >> 1) : gridDim.x;
+  const uint32_t tile_first = CTAS == 2 ? (blockIdx.x >> 1) : blockIdx.x;
+  const uint32_t tile_step = CTAS == 2 ? (gridDim.x >> 1) : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -494,7 +500,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = true;
       Tile tile;
       const uint32_t lead_full0 = CTAS == 2 ? map_to_cta(&full[0], 0) : 0u;   // the leader CTA's first full barrier
-      for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step) {
+      for (uint32_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step) {
         if (MODE != ESTMM && tile.skip) continue;
         for (int kb = 0; kb < tile.num_kb; ++kb) {
           if (!(ok = mbar_wait_fast(&empty[stage], phase ^ 1, abort_flag, p.status, 1, p.wait_limit_ns))) break;
@@ -573,7 +579,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = true;
       Tile tile;
       int it = -1;
-      for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step) {
+      for (uint32_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step) {
         if (MODE != ESTMM && tile.skip) continue;
         ++it;
         const int acc = it & 1;
@@ -619,7 +625,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     bool ok = true;
     Tile tile;
     int it = -1;
-    for (int64_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step) {
+    for (uint32_t t = tile_first; ok && get_tile<BN, MODE, CTAS>(p, t, rank, tile); t += tile_step) {
       if (MODE != ESTMM && tile.skip) continue;
       ++it;
       const int acc = it & 1;
@@ -996,6 +1002,8 @@ int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int6
   p.epilogue = epilogue; p.act = act; p.is_bf16 = is_bf16;
   p.status = status_word(); p.debug = tc_debug_flags(); p.wait_limit_ns = wait_limit_ns();
   const int64_t NT = ceil_div(n_out, BN);
+  HEXA_REQUIRE((row_cap / BLOCK_M + E + 1) * NT < (int64_t)0x7fffffff, "hexa_esmm: too many output tiles for a 32-bit tile index");
+  p.nt = (uint32_t)NT;
   const int ew = epi_warps_for(ceil_div(k, BLOCK_K));
   if (ctas == 2) {
     const int64_t max_tiles = p.max_pairs * NT;
@@ -1082,6 +1090,10 @@ int estmm_tc_launch(const void* pp, int64_t ldp, const void* q, int64_t ldq, con
   p.splits = splits; p.partial = static_cast<float*>(workspace);
   p.status = status_word(); p.debug = tc_debug_flags(); p.wait_limit_ns = wait_limit_ns();
   const int64_t max_tiles = (int64_t)E * ceil_div(m, BLOCK_M * ctas) * ceil_div(n, BN) * splits;
+  HEXA_REQUIRE(max_tiles < (int64_t)0x7fffffff, "hexa_estmm: too many output tiles for a 32-bit tile index");
+  p.nt = (uint32_t)ceil_div(n, BN);
+  p.per_expert = (uint32_t)(ceil_div(m, BLOCK_M * ctas) * ceil_div(n, BN) * splits);
+  p.total_tiles = (uint32_t)max_tiles;
   // ESTMM stores straight from registers; the two output maps are unused placeholders
   int rc;
   const int ew = epi_warps_for(row_cap / BLOCK_K / (E * (int64_t)splits));
