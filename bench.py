@@ -492,11 +492,20 @@ def multi_gpu_parity(rank, world, dev, data_centric, proportion, dtype_name="bfl
     xs = [torch.randn(T, d, generator=torch.Generator().manual_seed(100 + r)).to(dtype) for r in range(world)]
     x = xs[rank].to(dev).requires_grad_(True)
     ids_used, h = [], x
-    for i in range(L):
-        h, _ = m(i, h)
-        ids_used.append(torch.stack([t.cpu() for t in m.dispatch_params.indices_], dim=1))
-    h.float().sum().backward()
-    torch.cuda.synchronize()
+    # the small module cuts its tokens into as many chunks as the timed step does (model-centric mode)
+    least = os.environ.get("HEXA_MC_MIN_CHUNK_TOKENS")
+    os.environ["HEXA_MC_MIN_CHUNK_TOKENS"] = "64"
+    try:
+        for i in range(L):
+            h, _ = m(i, h)
+            ids_used.append(torch.stack([t.cpu() for t in m.dispatch_params.indices_], dim=1))
+        h.float().sum().backward()
+        torch.cuda.synchronize()
+    finally:
+        if least is None:
+            del os.environ["HEXA_MC_MIN_CHUNK_TOKENS"]
+        else:
+            os.environ["HEXA_MC_MIN_CHUNK_TOKENS"] = least
     all_ids = [[None] * world for _ in range(L)]
     for i in range(L):
         dist.all_gather_object(all_ids[i], ids_used[i])
@@ -766,6 +775,9 @@ def main():
                                                           "device, where an optimizer would consume them"),
                     parity=parity, scale_timeline=timeline,
                     gpu_launches=launches, kernels=kernels, roofline=roofline, cpu_baseline=cpu_baseline, clocks=clocks)
+        if world > 1 and args.mode == "model":
+            from hexa_moe_b200.impls.layers import token_chunks
+            line["config"]["token_chunks"] = len(token_chunks([T] * world)[0]) - 1
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

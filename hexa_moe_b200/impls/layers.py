@@ -94,37 +94,89 @@ def reduce_scatter_hidden_avg(full: Tensor, split: List[int], rank: int, group) 
     return out
 
 
-def all_gather_tokens(t: Tensor, sizes: List[int], group) -> Tensor:
-    """Concatenate every rank's rows ([sizes[r], ...] on rank r) in rank order."""
+class _InFlight:
+    """A collective that was started with async_op=True.  wait() makes the current stream (NCCL) or the host (gloo) wait
+    for it and returns its result; until then the object keeps the buffers of the collective alive."""
+
+    def __init__(self, work, finish, keep=()):
+        self.work, self.finish, self.keep = work, finish, keep
+
+    def wait(self) -> Tensor:
+        if self.work is not None:
+            self.work.wait()
+        out = self.finish()
+        self.work = self.finish = None
+        self.keep = ()
+        return out
+
+
+def all_gather_tokens_start(t: Tensor, sizes: List[int], group) -> _InFlight:
+    """Start concatenating every rank's rows ([sizes[r], ...] on rank r) in rank order."""
     W = len(sizes)
     if W == 1:
-        return t
+        return _InFlight(None, lambda: t)
     bound = max(sizes)
     if all(s == bound for s in sizes):
         out = t.new_empty((W * bound,) + tuple(t.shape[1:]))
-        dist.all_gather_into_tensor(out, t.contiguous(), group=group)
-        return out
+        src = t.contiguous()
+        return _InFlight(dist.all_gather_into_tensor(out, src, group=group, async_op=True), lambda: out, (src,))
     padded = t.new_zeros((bound,) + tuple(t.shape[1:]))
     padded[: t.shape[0]].copy_(t)
     buf = t.new_empty((W, bound) + tuple(t.shape[1:]))
-    dist.all_gather_into_tensor(buf.view((W * bound,) + tuple(t.shape[1:])), padded, group=group)
-    return torch.cat([buf[r, : sizes[r]] for r in range(W)], dim=0)
+    work = dist.all_gather_into_tensor(buf.view((W * bound,) + tuple(t.shape[1:])), padded, group=group, async_op=True)
+    return _InFlight(work, lambda: torch.cat([buf[r, : sizes[r]] for r in range(W)], dim=0), (padded,))
+
+
+def all_gather_tokens(t: Tensor, sizes: List[int], group) -> Tensor:
+    return all_gather_tokens_start(t, sizes, group).wait()
+
+
+def reduce_scatter_tokens_sum_start(t: Tensor, sizes: List[int], rank: int, group) -> _InFlight:
+    """Start the sum over ranks of `t` [sum(sizes), ...]; the result is this rank's token chunk."""
+    W = len(sizes)
+    if W == 1:
+        return _InFlight(None, lambda: t)
+    lo = sum(sizes[:rank])
+    bound = max(sizes)
+    src = t.contiguous()
+    if _is_nccl(group) and all(s == bound for s in sizes):
+        out = t.new_empty((bound,) + tuple(t.shape[1:]))
+        return _InFlight(dist.reduce_scatter_tensor(out, src, op=dist.ReduceOp.SUM, group=group, async_op=True),
+                         lambda: out, (src,))
+    return _InFlight(dist.all_reduce(src, op=dist.ReduceOp.SUM, group=group, async_op=True),
+                     lambda: src[lo: lo + sizes[rank]].contiguous())
 
 
 def reduce_scatter_tokens_sum(t: Tensor, sizes: List[int], rank: int, group) -> Tensor:
-    """Sum over ranks of `t` [sum(sizes), ...], returning this rank's token chunk."""
-    W = len(sizes)
-    if W == 1:
-        return t
-    lo = sum(sizes[:rank])
-    bound = max(sizes)
-    if _is_nccl(group) and all(s == bound for s in sizes):
-        out = t.new_empty((bound,) + tuple(t.shape[1:]))
-        dist.reduce_scatter_tensor(out, t.contiguous(), op=dist.ReduceOp.SUM, group=group)
-        return out
-    red = t.contiguous()
-    dist.all_reduce(red, op=dist.ReduceOp.SUM, group=group)
-    return red[lo: lo + sizes[rank]].contiguous()
+    return reduce_scatter_tokens_sum_start(t, sizes, rank, group).wait()
+
+
+def token_chunks(sizes: List[int]) -> List[List[int]]:
+    """Model-centric mode moves every token to every rank and the partial outputs back; cutting each rank's tokens into
+    chunks lets the transfers of one chunk run beside the GEMMs of another.  Returns the per-rank cut points
+    [[0, ..., sizes[r]] for r], the same number of chunks on every rank: HEXA_MC_CHUNKS, fewer when a chunk would hold
+    less than HEXA_MC_MIN_CHUNK_TOKENS (default 2048) tokens of the smallest rank.  The default is one chunk: then only
+    the reduce-scatter of the input gradients overlaps (with the two weight-gradient GEMMs of its layer), which was the
+    fastest setting at 2 GPUs and within 1 % of two chunks at 8; more chunks hide more of the transfers but their
+    GEMMs are shorter, padded per chunk and kept off the SMs reserved for NCCL.  HEXA_MC_CHUNKS=0: one chunk and
+    every collective waited for where it is issued (the reference's order, layers.py:131-211, 317-396)."""
+    want = max(1, int(os.environ.get("HEXA_MC_CHUNKS", "1")))
+    least = max(1, int(os.environ.get("HEXA_MC_MIN_CHUNK_TOKENS", "2048")))
+    C = max(1, min(want, min(sizes) // least)) if len(sizes) > 1 else 1
+    return [[s * c // C for c in range(C + 1)] for s in sizes]
+
+
+def _reserve_comm_sms(on: bool, t: Tensor, group):
+    """While NCCL kernels are meant to run beside the persistent GEMMs, keep the GEMMs off HEXA_COMM_SMS SMs
+    (default 16): their tile schedule is static, so a CTA that has to wait for an SM held by NCCL delays its launch."""
+    if not (t.is_cuda and _is_nccl(group)):
+        return
+    from .. import _lib
+    n = 0
+    reserve = int(os.environ.get("HEXA_COMM_SMS", "16"))
+    if on and reserve > 0:
+        n = max(2, torch.cuda.get_device_properties(t.device).multi_processor_count - reserve)
+    _lib.lib().hexa_set_sm_limit(n)
 
 
 def gather_token_counts(n: int, device, group) -> List[int]:
@@ -302,18 +354,33 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
             ctx.local_w = (w1, w2) if W == 1 else None
         else:
             # model-centric: every rank sees all tokens and owns a slice of the hidden dimension
+            # (the token chunks are gathered up front; the partial outputs of chunk c travel while chunk c+1 computes)
             sizes = gather_token_counts(T, x.device, cfg.group)
-            x_all = all_gather_tokens(x, sizes, cfg.group)
-            ids_all = all_gather_tokens(ids.t().contiguous(), sizes, cfg.group).t().contiguous()   # [k, T_w]
+            cuts = token_chunks(sizes)
+            C = len(cuts[0]) - 1
+            chunk_sizes = [[cuts[r][c + 1] - cuts[r][c] for r in range(W)] for c in range(C)]
+            mine = cuts[rank]
+            ids_t = ids.t().contiguous()                                                    # [T, k]
+            arriving = [(all_gather_tokens_start(x[mine[c]: mine[c + 1]], chunk_sizes[c], cfg.group),
+                         all_gather_tokens_start(ids_t[mine[c]: mine[c + 1]], chunk_sizes[c], cfg.group)) for c in range(C)]
             loc = cfg.local_dim_list_all[rank][stage]
             w1 = _cast(fc1_w.detach()[:, :loc], dtype)
             w2 = _cast(fc2_w.detach()[:, :loc], dtype)
             b1 = None if fc1_bias is None else fc1_bias.detach()[:, :loc]
             b2 = fc2_bias.detach() if (fc2_bias is not None and rank == 0) else None       # bias enters the sum once
-            y_all, st = cfg.backend.moe_forward(x_all, ids_all, w1, w2, b1, b2, cfg.act_id, act_fn=cfg.activation_fn,
-                                                route_major=True, need_state=need_state)
-            y = reduce_scatter_tokens_sum(y_all, sizes, rank, cfg.group)
-            ctx.sizes = sizes
+            _reserve_comm_sms(C > 1, x, cfg.group)
+            st, leaving = [], []
+            for c in range(C):
+                x_all = arriving[c][0].wait()
+                ids_all = arriving[c][1].wait().t().contiguous()                            # [k, tokens of the chunk]
+                y_all, st_c = cfg.backend.moe_forward(x_all, ids_all, w1, w2, b1, b2, cfg.act_id, act_fn=cfg.activation_fn,
+                                                      route_major=True, need_state=need_state)
+                leaving.append(reduce_scatter_tokens_sum_start(y_all, chunk_sizes[c], rank, cfg.group))
+                st.append(st_c)
+            _reserve_comm_sms(False, x, cfg.group)
+            parts = [p.wait() for p in leaving]
+            y = parts[0] if C == 1 else torch.cat(parts, dim=0)
+            ctx.sizes = (chunk_sizes, mine)
             ctx.local_w = (w1, w2)
         ctx.state = st
         return y.reshape(T, -1)
@@ -367,12 +434,29 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
                 else:
                     (dw2, db2), (dw1, db1) = red["fc2"], red["fc1"]
         else:
-            sizes = ctx.sizes
+            # per chunk: input gradients first, their reduce-scatter then runs beside the two weight-gradient GEMMs
+            chunk_sizes, mine = ctx.sizes
+            C = len(chunk_sizes)
             w1, w2 = ctx.local_w
-            dy_all = all_gather_tokens(dy, sizes, cfg.group)
-            dh, dw2, db2 = be.moe_backward_fc2(st, dy_all, w2, cfg.act_id, has_b2=ctx.has_b2, grad_dtype=w2_dt)
-            dx_all, dw1, db1 = be.moe_backward_fc1(st, dh, w1, has_b1=ctx.has_b1, grad_dtype=w1_dt)
-            dx = reduce_scatter_tokens_sum(dx_all, sizes, rank, cfg.group)
+            arriving = [all_gather_tokens_start(dy[mine[c]: mine[c + 1]], chunk_sizes[c], cfg.group) for c in range(C)]
+            grads, leaving = None, []
+            _reserve_comm_sms(C > 1, dy, cfg.group)
+            for c in range(C):
+                dx_all, kept = be.moe_backward_inputs(st[c], arriving[c].wait(), w1, w2, cfg.act_id)
+                leaving.append(reduce_scatter_tokens_sum_start(dx_all, chunk_sizes[c], rank, cfg.group))
+                if os.environ.get("HEXA_MC_CHUNKS") == "0":
+                    done = leaving[-1].wait()
+                    leaving[-1] = _InFlight(None, lambda done=done: done)
+                else:
+                    _reserve_comm_sms(W > 1, dy, cfg.group)
+                grads = be.moe_backward_params(st[c], kept, has_b1=ctx.has_b1, has_b2=ctx.has_b2, grad_dtype=w1_dt, into=grads)
+                st[c] = None
+            _reserve_comm_sms(False, dy, cfg.group)
+            dw1, dw2, db1, db2 = grads
+            if dw2.dtype != w2_dt:
+                dw2 = dw2.to(w2_dt)
+            parts = [p.wait() for p in leaving]
+            dx = parts[0] if C == 1 else torch.cat(parts, dim=0)
         ctx.state = None
         cfg.stage = stage - 1
         if db1 is not None:

@@ -436,6 +436,42 @@ def moe_backward_fc1(st: LayerState, dh, w1, has_b1=True, grad_dtype=None, engin
     return dx, dw1, db1
 
 
+def moe_backward_inputs(st: LayerState, dy, w1, w2, act_id: int, engine=L.ENGINE_AUTO):
+    """The input-gradient half of the layer backward, ahead of the parameter gradients: returns (dx [T,d], kept) where
+    `kept` = (dys, dh) is what moe_backward_params needs.  A caller that has to send dx to other ranks can start the
+    transfer after this call and let it run beside the two weight-gradient GEMMs."""
+    r = st.routing
+    dys = gather_rows(dy.contiguous(), r)
+    if act_id >= 0:
+        dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_DACT, act_id, aux=st.y1, engine=engine, tag="fc2_dgrad_dact")
+    else:
+        dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_LINEAR, engine=engine, tag="fc2_dgrad")
+        dh.mul_(st.act_grad)
+        mask_pad_rows(dh, r)
+    dxs = esmm(dh, w1, L.B_KN, r, None, L.EPI_LINEAR, engine=engine, tag="fc1_dgrad")
+    return combine_rows(dxs, r), (dys, dh)
+
+
+def moe_backward_params(st: LayerState, kept, has_b1=True, has_b2=True, grad_dtype=None, engine=L.ENGINE_AUTO, into=None):
+    """(dw1 [E,H,d], dw2 [E,H,d_out], db1 [E,H] | None, db2 [E,d_out] | None) from what moe_backward_inputs kept.
+    into: the same four from an earlier call over other tokens of the same layer; this call's gradients are added to
+    them in place (the weight GEMMs accumulate onto their output) and they are returned."""
+    r = st.routing
+    dys, dh = kept
+    if into is None:
+        dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine, tag="dw2")
+        dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine, tag="dw1")
+        return dw1, dw2, (ess(dh, r) if has_b1 else None), (ess(dys, r) if has_b2 else None)
+    dw1, dw2, db1, db2 = into
+    estmm(st.h, dys, r, out=dw2, beta=1, engine=engine, tag="dw2")
+    estmm(dh, st.xs, r, out=dw1, beta=1, engine=engine, tag="dw1")
+    if has_b1:
+        db1 += ess(dh, r)
+    if has_b2:
+        db2 += ess(dys, r)
+    return dw1, dw2, db1, db2
+
+
 def moe_backward(st: LayerState, dy, w1, w2, act_id: int, has_b1=True, has_b2=True, grad_dtype=None,
                  engine=L.ENGINE_AUTO):
     """Gradients of moe_forward.  Returns (dx [T,d], dw1 [E,H,d], dw2 [E,H,d_out], db1 [E,H] | None,

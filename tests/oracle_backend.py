@@ -43,3 +43,20 @@ def moe_backward_fc1(st, dh, w1, has_b1=True, grad_dtype=None, engine=0, ranks=1
     if after_dw is not None:
         after_dw(dw1, db1)
     return r["dx"].to(st.x.dtype), dw1, db1
+
+
+def moe_backward_inputs(st, dy, w1, w2, act_id, engine=0):
+    r = _full(st, dy)
+    return r["dx"].to(st.x.dtype), (st, dy)
+
+
+def moe_backward_params(st, kept, has_b1=True, has_b2=True, grad_dtype=None, engine=0, into=None):
+    r = st.res
+    gd = grad_dtype or st.x.dtype
+    new = (r["dw1"].to(gd), r["dw2"].to(gd), r["db1"].float() if has_b1 else None, r["db2"].float() if has_b2 else None)
+    if into is None:
+        return new
+    for acc, g in zip(into, new):
+        if g is not None:
+            acc += g
+    return into

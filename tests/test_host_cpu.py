@@ -280,3 +280,19 @@ def test_bench_arms_describe_the_same_configuration():
     assert bench.cpu_sample_text(2, 64).startswith("16384 tokens (seed 0) top-2 over 8 of the 64 experts")
     assert set(bench.TRAFFIC_RATIO) == {"esmm:fc1_forward_act", "esmm:fc2_forward", "estmm:dw2", "esmm:fc2_dgrad_dact",
                                         "estmm:dw1", "esmm:fc1_dgrad"}
+
+
+def test_token_chunks_are_the_same_count_on_every_rank(monkeypatch):
+    from hexa_moe_b200.impls.layers import token_chunks
+    monkeypatch.setenv("HEXA_MC_CHUNKS", "4")
+    monkeypatch.setenv("HEXA_MC_MIN_CHUNK_TOKENS", "10")
+    assert token_chunks([100]) == [[0, 100]]                               # one rank: nothing to overlap
+    cuts = token_chunks([100, 41])
+    assert cuts == [[0, 25, 50, 75, 100], [0, 10, 20, 30, 41]]             # 41 // 10 = 4 chunks fit the smallest rank
+    assert token_chunks([100, 25]) == [[0, 50, 100], [0, 12, 25]]          # only two chunks of >= 10 tokens fit
+    assert token_chunks([100, 0]) == [[0, 100], [0, 0]]                    # a rank without tokens: no cutting
+    monkeypatch.delenv("HEXA_MC_CHUNKS"); monkeypatch.delenv("HEXA_MC_MIN_CHUNK_TOKENS")
+    assert token_chunks([16384] * 8)[0] == [0, 16384]                      # default: one chunk
+    monkeypatch.setenv("HEXA_MC_CHUNKS", "2")
+    assert token_chunks([16384] * 8)[0] == [0, 8192, 16384]
+    assert token_chunks([384] * 2)[0] == [0, 384]                          # too few tokens to cut

@@ -132,6 +132,13 @@ def test_model_centric_two_gpus(proportion, dtype_name):
     _run(False, proportion, dtype_name)
 
 
+@pytest.mark.parametrize("chunks", ["0", "3"])
+def test_model_centric_two_gpus_token_chunks(chunks):
+    """Tokens cut into three chunks per rank (collectives of one chunk beside the GEMMs of another, weight gradients
+    accumulated over the chunks), and the in-line order with one chunk: same results."""
+    _run(False, [0.375, 0.625], "bfloat16", env={"HEXA_MC_CHUNKS": chunks, "HEXA_MC_MIN_CHUNK_TOKENS": "64"})
+
+
 def test_data_centric_two_gpus_gradients_returned_through_autograd():
     """HEXA_DEFER_GRADS=0 on real devices: backward waits for the side-stream reduction and returns the slices."""
     _run(True, None, "bfloat16", env={"HEXA_DEFER_GRADS": "0"})

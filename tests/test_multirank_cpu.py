@@ -31,9 +31,10 @@ def _full_params(E, d, H, n_layers, seed=0):
     return P
 
 
-def _worker(rank, world, port, data_centric, proportion, tokens_per_rank, q, defer_grads="1"):
+def _worker(rank, world, port, data_centric, proportion, tokens_per_rank, q, defer_grads="1", env=None):
     sys.path.insert(0, ROOT); sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), HEXA_DEFER_GRADS=defer_grads)
+    os.environ.update(env or {})
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         import oracle_backend
@@ -111,12 +112,12 @@ def _worker(rank, world, port, data_centric, proportion, tokens_per_rank, q, def
         dist.destroy_process_group()
 
 
-def _run(data_centric, proportion, tokens_per_rank, defer_grads="1"):
+def _run(data_centric, proportion, tokens_per_rank, defer_grads="1", env=None):
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, data_centric, proportion, tokens_per_rank, q, defer_grads))
+    procs = [ctx.Process(target=_worker, args=(r, world, port, data_centric, proportion, tokens_per_rank, q, defer_grads, env))
              for r in range(world)]
     for p in procs:
         p.start()
@@ -139,6 +140,13 @@ def test_data_centric_two_ranks(proportion):
 @pytest.mark.parametrize("proportion,tokens", [(None, [32, 32]), ([0.3, 0.7], [24, 40])])
 def test_model_centric_two_ranks(proportion, tokens):
     _run(False, proportion, tokens)
+
+
+@pytest.mark.parametrize("proportion,tokens,chunks", [(None, [32, 32], 2), ([0.3, 0.7], [24, 40], 3), (None, [5, 2], 4)])
+def test_model_centric_token_chunks(proportion, tokens, chunks):
+    """The tokens of every rank cut into chunks whose transfers overlap the other chunks' GEMMs: same results; ragged
+    chunks when the token counts differ or do not divide, fewer chunks than asked when a rank has too few tokens."""
+    _run(False, proportion, tokens, env={"HEXA_MC_CHUNKS": str(chunks), "HEXA_MC_MIN_CHUNK_TOKENS": "1"})
 
 
 @pytest.mark.parametrize("proportion", [None, [0.7, 0.3]])
