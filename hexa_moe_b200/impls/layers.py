@@ -169,7 +169,7 @@ def token_chunks(sizes: List[int]) -> List[List[int]]:
 def _reserve_comm_sms(on: bool, t: Tensor, group):
     """While NCCL kernels are meant to run beside the persistent GEMMs, keep the GEMMs off HEXA_COMM_SMS SMs
     (default 16): their tile schedule is static, so a CTA that has to wait for an SM held by NCCL delays its launch."""
-    if not (t.is_cuda and _is_nccl(group)):
+    if not (t.is_cuda and _world(group) > 1 and _is_nccl(group)):
         return
     from .. import _lib
     n = 0

@@ -92,6 +92,29 @@ def test_moe_depth_against_oracle(dtype, k, tol):
     assert m.dispatch_params.stage == -1                          # decremented in backward like the reference
 
 
+def test_model_centric_module_on_one_gpu_matches_data_centric():
+    """data_centric=False without a process group: the model-centric branch (input gradients first, then the parameter
+    gradients) must give what the data-centric branch gives on the same weights and tokens."""
+    d, E, T, k = 64, 6, 900, 2
+    outs = []
+    for data_centric in (True, False):
+        torch.manual_seed(11)
+        m = _toy(k=k, d=d, E=E, data_centric=data_centric)
+        with torch.no_grad():
+            for n_, p in m.named_parameters():
+                p.normal_(0, 0.5 if "gates" in n_ else (0.1 if p.dim() < 3 else 0.15))
+        m = m.bfloat16().cuda().eval()
+        x = torch.randn(T, d, generator=torch.Generator().manual_seed(4)).bfloat16().cuda().requires_grad_(True)
+        y, _ = m(2, x)
+        y2, _ = m(3, y)
+        y2.float().square().mean().backward()
+        outs.append([y2.detach(), x.grad] + [dict(m.named_parameters())[n_].grad for n_ in
+                                             ("batched_fc1_w.0", "batched_fc2_w.1", "batched_fc1_bias.1", "batched_fc2_bias.0")])
+    for a, b in zip(*outs):
+        assert a is not None and b is not None
+        assert rel_err(b, a) < 1e-2        # same kernels in another order; bf16 weight gradients round once either way
+
+
 def test_training_mode_autocast_and_options():
     torch.manual_seed(0)
     m = _toy(k=2, d=64, E=8, result_func=lambda t: t * 2.0, is_gshard_loss=False).cuda().train()

@@ -282,3 +282,29 @@ def test_dense_ffn_gradients_are_averaged_over_ranks(defer):
                 p.kill()
     for rank, msg in res:
         assert msg == "ok", f"rank {rank}: {msg}"
+
+
+def test_model_centric_without_a_process_group():
+    """A single process that never initialised torch.distributed runs the model-centric branch as well: the collectives
+    pass their input through and nothing asks the (absent) process group for its backend."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_backend
+    from hexa_moe import moe as hmoe
+    assert not dist.is_initialized()
+    E, d, H, k, L, T = 4, 16, 64, 2, 2, 24
+    outs = []
+    for data_centric in (True, False):
+        torch.manual_seed(0)
+        m = hmoe.MoE_Cascaded(gate_type={'type': 'top', 'k': k, 'fp32_gate': True}, model_dim_list=[d] * L, moe_idx_list=[0, 1],
+                              mlp_ratio=H // d, mlp_proportion=None, num_global_experts=E, total_depth=L,
+                              data_centric=data_centric, activation_fn=lambda t: F.gelu(t))
+        m.dispatch_params.backend = oracle_backend
+        m.eval()
+        x = torch.randn(T, d, generator=torch.Generator().manual_seed(5)).requires_grad_(True)
+        h = x
+        for i in range(L):
+            h, _ = m(i, h)
+        h.sum().backward()
+        outs.append((h.detach(), x.grad, m.batched_fc1_w[0].grad, m.batched_fc2_bias[1].grad))
+    for a, b in zip(*outs):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
