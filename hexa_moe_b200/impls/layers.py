@@ -240,6 +240,8 @@ class MLP_Implement(torch.autograd.Function):
     def forward(ctx: Any, config: Any, tokens_input: Tensor, fc1_w, fc2_w, fc1_bias, fc2_bias):
         ctx.config = config
         assert tokens_input.shape[1] == fc1_w.shape[1] and fc1_w.shape[0] == fc2_w.shape[0]
+        if getattr(config, "dense_reducer", None) is not None:
+            config.dense_reducer.drop_stale()
         ctx.params = (fc1_w, fc2_w, fc1_bias, fc2_bias)
         dtype = tokens_input.dtype
         ctx.has_b1, ctx.has_b2 = fc1_bias is not None, fc2_bias is not None

@@ -143,6 +143,13 @@ class DenseGradReducer:
             self._queued = True
             torch.autograd.Variable._execution_engine.queue_callback(self._flush)
 
+    def drop_stale(self):
+        """Called from a dense layer's forward: gradients still queued here outside a backward pass were left by a
+        backward pass that raised before its end-of-pass callback ran; they belong to no step, and the callback flag
+        they left set would keep every later pass from queueing its own."""
+        if self._queued and not PipelineSharedCache._in_backward():
+            self._open, self._done, self._queued = {}, [], False
+
     def _launch(self, dtype):
         flat, fill, entries = self._open.pop(dtype)
         if fill == 0:

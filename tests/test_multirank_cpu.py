@@ -233,6 +233,23 @@ def _dense_worker(rank, world, port, defer, q):
                 if n_.startswith("mlp_"):
                     p.normal_(0, 0.3)
         x = torch.randn(24, d, generator=torch.Generator().manual_seed(50 + rank))
+        if defer == "1":
+            # a backward pass that raises after the dense layers queued their gradients must not leak into the next step
+            class _Boom(torch.autograd.Function):
+                @staticmethod
+                def forward(ctx, t):
+                    return t.clone()
+
+                @staticmethod
+                def backward(ctx, g):
+                    raise RuntimeError("boom")
+            h = _Boom.apply(x.clone().requires_grad_(True))
+            for depth in range(2):
+                h, _ = m(depth, h)
+            with pytest.raises(RuntimeError, match="boom"):
+                h.pow(2).sum().backward()
+            for p in m.parameters():
+                p.grad = None
         h = x
         for depth in range(2):               # the two dense depths
             h, aux = m(depth, h)
