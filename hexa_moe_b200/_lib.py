@@ -43,6 +43,8 @@ SIGNATURES = {
     "hexa_esmm": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, vp, i64, vp, i64, vp, vp, vp, vp, ci, i64, i64, i64, ci, ci, ci, ci, vp]),
     "hexa_esmm_experts": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, vp, i64, vp, i64, vp, vp, vp, vp, ci, i64, i64, i64, ci, ci, ci, ci,
                                ci, ci, vp]),
+    "hexa_esmm_ess": (ci, [vp, i64, vp, ci, i64, i64, vp, i64, vp, i64, vp, i64, vp, vp, vp, vp, ci, i64, i64, i64, ci, ci, ci, ci,
+                           vp, i64, vp, sz, vp]),
     "hexa_estmm_workspace_bytes": (sz, [ci, i64, i64, i64, ci]),
     "hexa_estmm": (ci, [vp, i64, vp, i64, vp, ci, i64, i64, i64, vp, i64, i64, i64, i64, ci, ci, ci, ci, vp, sz, vp]),
     "hexa_estmm_scatter": (ci, [vp, i64, vp, i64, vp, ci, i64, i64, i64, vp, ci, i64, i64, i64, ci, ci, vp]),

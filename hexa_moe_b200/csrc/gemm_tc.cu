@@ -76,6 +76,8 @@ struct Params {
   int beta;         // ESTMM: accumulate into out
   int splits;       // ESTMM: > 1 = every expert's row segment is cut into this many chunks, each its own tile, whose fp32
   float* partial;   //        partial results [splits, E, m, n] go here and are added in chunk order by estmm_reduce_kernel
+  float* colsum;    // ESMM, optional: fp32 [row_capacity / 128, n]; row b receives the column sums of the 128 output rows
+                    // of block b, taken from the values as they are stored (after rounding to the 16-bit type)
   int debug;        // measurement / test aid (HEXA_TC_DEBUG, hexa_set_tc_debug): bit 0 = the producer skips the TMA loads and
                     // arrives in their place, bit 1 = the MMA thread skips the MMAs, bit 2 = the producer neither loads
                     // nor arrives, so that every wait of the pipeline runs into its limit
@@ -767,6 +769,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               bulk_commit();
             }
           }
+          if (p.colsum != nullptr && !(p.debug & 32)) {
+            // Column sums of the block that now sits in the staging tile (the output as stored).  The warp whose TMEM
+            // quadrant is q takes the 16-byte chunk q of every row: lane = (row mod 8) * 4 + 32-bit word within the
+            // chunk (two columns), 16 rows per lane, then the eight row classes meet through three shuffles.  The eight
+            // rows of one load fall into eight different groups of four banks (rows r, r+1 differ by 64 bytes, rows
+            // r, r+2 by the swizzle): one conflict-free 128-byte wavefront per load.  Nothing else is synchronised:
+            // every thread has finished reading before it arrives at the barrier that precedes the next write of the buffer.
+            const int w4 = lane & 3, ro = lane >> 2;
+            const uint8_t* src = buf + ro * 64 + ((q ^ ((ro >> 1) & 3)) << 4) + w4 * 4;   // (r >> 1) & 3 == (ro >> 1) & 3 for r = 8 i + ro
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const uint32_t v = *reinterpret_cast<const uint32_t*>(src + i * 512);
+              s0 += unpack_lo(v, is_bf16);
+              s1 += unpack_hi(v, is_bf16);
+            }
+#pragma unroll
+            for (int d = 4; d < 32; d <<= 1) {
+              s0 += __shfl_xor_sync(0xffffffffu, s0, d);
+              s1 += __shfl_xor_sync(0xffffffffu, s1, d);
+            }
+            const int64_t col = gcol + q * 8 + w4 * 2;
+            if (ro == 0 && col < p.n) {
+              float* dst = p.colsum + (int64_t)(tile.row0 / BLOCK_M) * p.n + col;
+              dst[0] = s0;
+              if (col + 1 < p.n) dst[1] = s1;
+            }
+          }
         }
       }
       // accumulator drained: hand it back to the (leader's) MMA warp
@@ -953,7 +983,7 @@ int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int6
                    const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
                    const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
                    const int32_t* pair_block, int E, int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue,
-                   int act, cudaStream_t stream, int e_begin, int e_end) {
+                   int act, cudaStream_t stream, int e_begin, int e_end, float* colsum) {
   if (row_cap == 0 || e_begin >= e_end) return HEXA_OK;
   const int is_bf16 = dtype == HEXA_BF16;
   const int BN = n_out > 128 ? 256 : 128;
@@ -999,7 +1029,7 @@ int esmm_tc_launch(const void* a, int64_t lda, const void* b, int b_layout, int6
   p.pair_block = pair_block; p.max_pairs = row_cap / (2 * BLOCK_M) + E;
   p.bias = bias; p.ldbias = ldbias; p.aux = aux; p.ldaux = ldaux; p.c = c; p.ldc = ldc;
   p.n = n_out; p.k = k; p.m = 0; p.E = E; p.e_begin = e_begin; p.e_end = e_end;
-  p.epilogue = epilogue; p.act = act; p.is_bf16 = is_bf16;
+  p.epilogue = epilogue; p.act = act; p.is_bf16 = is_bf16; p.colsum = colsum;
   p.status = status_word(); p.debug = tc_debug_flags(); p.wait_limit_ns = wait_limit_ns();
   const int64_t NT = ceil_div(n_out, BN);
   HEXA_REQUIRE((row_cap / BLOCK_M + E + 1) * NT < (int64_t)0x7fffffff, "hexa_esmm: too many output tiles for a 32-bit tile index");

@@ -72,6 +72,44 @@ extern "C" int hexa_esmm(const void* a, int64_t lda, const void* b, int b_layout
                            row_token, pair_block, E, row_cap, n_out, k, dtype, epilogue, act, engine, 0, E, stream_);
 }
 
+extern "C" int hexa_esmm_ess(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
+                             const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
+                             const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
+                             const int32_t* pair_block, int E, int64_t row_cap, int64_t n_out, int64_t k, int dtype, int epilogue,
+                             int act, int engine, float* sums, int64_t ld_sums, void* workspace, size_t workspace_bytes,
+                             void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  HEXA_REQUIRE(sums && workspace && ld_sums >= n_out, "hexa_esmm_ess: sums / workspace missing or ld_sums too small");
+  HEXA_REQUIRE(E > 0 && E <= 65535 && row_cap >= 0 && n_out > 0, "hexa_esmm_ess: bad sizes");
+  const size_t need = hexa_ess_workspace_bytes(row_cap, n_out);
+  if (workspace_bytes < need) {
+    set_error("hexa_esmm_ess: workspace %zu bytes < required %zu", workspace_bytes, need);
+    return HEXA_ERR_WORKSPACE;
+  }
+  const bool fused = a && b && c && engine != HEXA_ENGINE_SIMT &&
+                     esmm_tc_supported(a, lda, b, ldb, b_estride, aux, ldaux, c, ldc, bias, ldbias, n_out, dtype);
+  if (!fused) {   // same result in two passes: the GEMM, then ESS over its output
+    int rc = hexa_esmm_experts(a, lda, b, b_layout, ldb, b_estride, bias, ldbias, aux, ldaux, c, ldc, tile_expert, pad_offsets,
+                               row_token, pair_block, E, row_cap, n_out, k, dtype, epilogue, act, engine, 0, E, stream_);
+    if (rc != HEXA_OK) return rc;
+    return ess_launch(c, ldc, pad_offsets, E, row_cap, n_out, sums, ld_sums, dtype, (float*)workspace, stream);
+  }
+  // the checks of hexa_esmm_experts, then the tcgen05 launch with the block sums switched on
+  HEXA_REQUIRE(tile_expert && pad_offsets, "hexa_esmm_ess: null pointer");
+  HEXA_REQUIRE(row_cap % kRowTile == 0 && k > 0, "hexa_esmm_ess: bad sizes (row_capacity must be a multiple of %d)", kRowTile);
+  HEXA_REQUIRE(lda >= k && ldc >= n_out && (!aux || ldaux >= n_out) && (!bias || ldbias >= n_out), "hexa_esmm_ess: leading dimension too small");
+  HEXA_REQUIRE(b_layout == HEXA_B_NK || b_layout == HEXA_B_KN, "hexa_esmm_ess: bad b_layout %d", b_layout);
+  HEXA_REQUIRE(ldb >= (b_layout == HEXA_B_NK ? k : n_out), "hexa_esmm_ess: ldb too small");
+  HEXA_REQUIRE(epilogue >= HEXA_EPI_LINEAR && epilogue <= HEXA_EPI_DACT, "hexa_esmm_ess: bad epilogue %d", epilogue);
+  HEXA_REQUIRE(act >= HEXA_ACT_NONE && act <= HEXA_ACT_SILU, "hexa_esmm_ess: bad activation %d", act);
+  HEXA_REQUIRE(epilogue != HEXA_EPI_DACT || aux, "hexa_esmm_ess: HEXA_EPI_DACT needs the saved pre-activation in aux");
+  HEXA_CHECK_DEVICE_STATUS("hexa_esmm_ess");
+  int rc = esmm_tc_launch(a, lda, b, b_layout, ldb, b_estride, bias, ldbias, aux, ldaux, c, ldc, tile_expert, pad_offsets,
+                          row_token, pair_block, E, row_cap, n_out, k, dtype, epilogue, act, stream, 0, E, (float*)workspace);
+  if (rc != HEXA_OK) return rc;
+  return ess_finish((const float*)workspace, pad_offsets, E, n_out, sums, ld_sums, stream);
+}
+
 extern "C" size_t hexa_estmm_workspace_bytes(int E, int64_t row_cap, int64_t m, int64_t n, int dtype) {
   if (E <= 0 || row_cap <= 0 || m <= 0 || n <= 0 || (dtype != HEXA_F16 && dtype != HEXA_BF16)) return 0;
   return estmm_tc_workspace_bytes(E, row_cap, m, n);

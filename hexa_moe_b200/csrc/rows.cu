@@ -260,6 +260,7 @@ extern "C" size_t hexa_ess_workspace_bytes(int64_t row_cap, int64_t cols) {
 }
 
 namespace hexa {
+int ess_finish(const float* partial, const int32_t* pad_offsets, int E, int64_t cols, float* out, int64_t ldo, cudaStream_t stream);
 // Shared by hexa_ess and the entry points built on it: both passes on caller-provided scratch.
 int ess_launch(const void* src, int64_t src_ld, const int32_t* pad_offsets, int E, int64_t row_cap, int64_t cols,
                float* out, int64_t ldo, int dtype, float* partial, cudaStream_t stream) {
@@ -276,6 +277,10 @@ int ess_launch(const void* src, int64_t src_ld, const int32_t* pad_offsets, int 
     }
     HEXA_LAUNCH_CHECK("ess_partial");
   }
+  return ess_finish(partial, pad_offsets, E, cols, out, ldo, stream);
+}
+
+int ess_finish(const float* partial, const int32_t* pad_offsets, int E, int64_t cols, float* out, int64_t ldo, cudaStream_t stream) {
   dim3 grid2((unsigned)ceil_div(cols, 256), (unsigned)E);
   ess_final_kernel<<<grid2, 256, 0, stream>>>(partial, pad_offsets, cols, out, ldo);
   HEXA_LAUNCH_CHECK("ess_final");

@@ -411,7 +411,7 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
             packed = W > 1 and x_is_cuda(dy) and _is_nccl(cfg.group) and all(s_ == split[0] for s_ in split)
             kw = dict(ranks=W) if packed else {}
             kw2 = dict(kw, dw_out=cfg.cache.grad_buffer("fc2", stage)) if packed else {}
-            dh, dw2, db2 = be.moe_backward_fc2(st, dy, w2, cfg.act_id, has_b2=ctx.has_b2, grad_dtype=w2_dt, **kw2)
+            dh, dw2, db2 = be.moe_backward_fc2(st, dy, w2, cfg.act_id, has_b2=ctx.has_b2, grad_dtype=w2_dt, want_db1=ctx.has_b1, **kw2)
             # By default the reduced gradients are added to the parameters' .grad by a callback at the end of the
             # backward pass (nothing waits for the transfer); HEXA_DEFER_GRADS=0 returns them through autograd instead
             # (hooks, torch.autograd.grad and wrappers that inspect the returned gradients then see them).
@@ -444,7 +444,7 @@ class FusedMoE_Shared_CudaCore(torch.autograd.Function):
             grads, leaving = None, []
             _reserve_comm_sms(C > 1, dy, cfg.group)
             for c in range(C):
-                dx_all, kept = be.moe_backward_inputs(st[c], arriving[c].wait(), w1, w2, cfg.act_id)
+                dx_all, kept = be.moe_backward_inputs(st[c], arriving[c].wait(), w1, w2, cfg.act_id, want_db1=ctx.has_b1)
                 leaving.append(reduce_scatter_tokens_sum_start(dx_all, chunk_sizes[c], rank, cfg.group))
                 if os.environ.get("HEXA_MC_CHUNKS") == "0":
                     done = leaving[-1].wait()

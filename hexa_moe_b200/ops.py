@@ -7,6 +7,7 @@ device; no function has a CPU or PyTorch fallback.  Buffers in "sorted-row" layo
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -134,10 +135,13 @@ def combine_rows(src: torch.Tensor, r: Routing, out: Optional[torch.Tensor] = No
 def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Optional[torch.Tensor] = None,
          epilogue: int = L.EPI_LINEAR, act: int = L.ACT_NONE, aux: Optional[torch.Tensor] = None,
          out: Optional[torch.Tensor] = None, engine: int = L.ENGINE_AUTO, n_out: Optional[int] = None,
-         k: Optional[int] = None, tag: Optional[str] = None, experts: Optional[tuple] = None) -> torch.Tensor:
+         k: Optional[int] = None, tag: Optional[str] = None, experts: Optional[tuple] = None,
+         sums: Optional[torch.Tensor] = None) -> torch.Tensor:
     """c[row] = a[row] x b[expert(row)] with the fused epilogue.  b: [E, n_out, k] (B_NK) or [E, k, n_out] (B_KN);
     b may be a view with arbitrary expert / row strides (unit inner stride).  experts = (first, end): only the rows of
-    those experts are computed (the other rows of `out` are left as they are)."""
+    those experts are computed (the other rows of `out` are left as they are).  sums: a float32 [E, n_out] tensor that
+    receives the per-expert column sums of the output (ESS of `out`) from the same launch."""
+    global LAUNCHES
     if r.align % L.ROW_TILE:
         raise L.HexaError("esmm: routing must be aligned to 128 rows")
     if b.dim() != 3 or b.stride(2) != 1:
@@ -159,6 +163,18 @@ def esmm(a: torch.Tensor, b: torch.Tensor, b_layout: int, r: Routing, bias: Opti
     nbytes = es_ * (rows_ * k + r.num_experts * n_out * k + rows_ * n_out * (1 if epilogue == L.EPI_LINEAR else 2))
     e0, e1 = (0, r.num_experts) if experts is None else experts
     share = (e1 - e0) / max(r.num_experts, 1)        # work of a group, taken as its share of the experts
+    if sums is not None:
+        if experts is not None or sums.dtype != torch.float32 or tuple(sums.shape) != (r.num_experts, n_out) or sums.stride(1) != 1:
+            raise L.HexaError("esmm: sums must be float32 [E, n_out] and needs the full expert range")
+        ws = torch.empty(max(lib().hexa_ess_workspace_bytes(r.row_capacity, n_out), 4), dtype=torch.uint8, device=a.device)
+        with _Timed("esmm:" + (tag or "epilogue%d" % epilogue), 2.0 * rows_ * n_out * k, float(nbytes)):
+            check(lib().hexa_esmm_ess(ptr(a), _ld(a), ptr(b), b_layout, b.stride(1), b.stride(0), ptr(bias),
+                                      0 if bias is None else _ld(bias), ptr(aux), 0 if aux is None else _ld(aux), ptr(out),
+                                      _ld(out), ptr(r.tile_expert), ptr(r.pad_offsets), ptr(r.row_token), ptr(r.pair_block),
+                                      r.num_experts, r.row_capacity, n_out, k, dt(a), epilogue, act, engine, ptr(sums),
+                                      sums.stride(0), ptr(ws), ws.numel(), stream_of(a)), "hexa_esmm_ess")
+        LAUNCHES += 1          # the second pass of ESS over the block sums
+        return out
     with _Timed("esmm:" + (tag or "epilogue%d" % epilogue), 2.0 * rows_ * n_out * k * share, float(nbytes) * share):
         check(lib().hexa_esmm_experts(ptr(a), _ld(a), ptr(b), b_layout, b.stride(1), b.stride(0), ptr(bias),
                                       0 if bias is None else _ld(bias), ptr(aux), 0 if aux is None else _ld(aux), ptr(out),
@@ -345,6 +361,7 @@ class LayerState:
     y1: torch.Tensor      # fc1 pre-activation   [cap, H]
     h: torch.Tensor       # act(y1)              [cap, H]
     act_grad: Optional[torch.Tensor] = None   # act'(y1) when the activation is not a fused one
+    db1: Optional[torch.Tensor] = None        # ESS of the hidden gradient, when the GEMM that produced it summed it as well
 
 
 def _f32(t):
@@ -404,16 +421,26 @@ def moe_forward(x, ids, w1, w2, b1, b2, act_id: int, act_fn=None, route_major=Fa
     return y, (LayerState(r, xs, y1, h, g) if need_state else None)
 
 
+def _hidden_gradient(st: LayerState, dys, w2, act_id: int, engine, want_db1: bool):
+    """dh = dys W2^T * act'(y1) for a fused activation; with want_db1 the same launch leaves ESS(dh) in st.db1."""
+    r = st.routing
+    st.db1 = None
+    if want_db1 and os.environ.get("HEXA_FUSED_ESS", "1") != "0":
+        st.db1 = torch.empty(r.num_experts, w2.shape[1], dtype=torch.float32, device=dys.device)
+    return esmm(dys, w2, L.B_NK, r, None, L.EPI_DACT, act_id, aux=st.y1, engine=engine, tag="fc2_dgrad_dact", sums=st.db1)
+
+
 def moe_backward_fc2(st: LayerState, dy, w2, act_id: int, has_b2=True, grad_dtype=None, engine=L.ENGINE_AUTO, ranks=1,
-                     dw_out=None):
+                     dw_out=None, want_db1=False):
     """First half of the layer backward: (dh [cap,H] = dy W2^T * act'(y1), dw2 [E,H,d_out], db2 [E,d_out] | None).
-    Split from the fc1 half so a caller can start reducing dw2/db2 across ranks while fc1 runs."""
+    Split from the fc1 half so a caller can start reducing dw2/db2 across ranks while fc1 runs.  want_db1: the fc1
+    half will need the bias gradient ESS(dh); with a fused activation the GEMM that writes dh sums it on the way."""
     r = st.routing
     dys = gather_rows(dy.contiguous(), r)
     db2 = ess(dys, r) if has_b2 else None
     dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine, ranks=ranks, out=dw_out, tag="dw2")
     if act_id >= 0:
-        dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_DACT, act_id, aux=st.y1, engine=engine, tag="fc2_dgrad_dact")
+        dh = _hidden_gradient(st, dys, w2, act_id, engine, want_db1)
     else:
         dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_LINEAR, engine=engine, tag="fc2_dgrad")
         dh.mul_(st.act_grad)
@@ -427,7 +454,8 @@ def moe_backward_fc1(st: LayerState, dh, w1, has_b1=True, grad_dtype=None, engin
     host as soon as both parameter gradients are enqueued, before the input-gradient GEMM: a caller can start
     reducing them across ranks while that GEMM runs."""
     r = st.routing
-    db1 = ess(dh, r) if has_b1 else None
+    db1 = (st.db1 if st.db1 is not None else ess(dh, r)) if has_b1 else None
+    st.db1 = None
     dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine, ranks=ranks, out=dw_out, tag="dw1")
     if after_dw is not None:
         after_dw(dw1, db1)
@@ -436,14 +464,14 @@ def moe_backward_fc1(st: LayerState, dh, w1, has_b1=True, grad_dtype=None, engin
     return dx, dw1, db1
 
 
-def moe_backward_inputs(st: LayerState, dy, w1, w2, act_id: int, engine=L.ENGINE_AUTO):
+def moe_backward_inputs(st: LayerState, dy, w1, w2, act_id: int, engine=L.ENGINE_AUTO, want_db1=False):
     """The input-gradient half of the layer backward, ahead of the parameter gradients: returns (dx [T,d], kept) where
     `kept` = (dys, dh) is what moe_backward_params needs.  A caller that has to send dx to other ranks can start the
     transfer after this call and let it run beside the two weight-gradient GEMMs."""
     r = st.routing
     dys = gather_rows(dy.contiguous(), r)
     if act_id >= 0:
-        dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_DACT, act_id, aux=st.y1, engine=engine, tag="fc2_dgrad_dact")
+        dh = _hidden_gradient(st, dys, w2, act_id, engine, want_db1)
     else:
         dh = esmm(dys, w2, L.B_NK, r, None, L.EPI_LINEAR, engine=engine, tag="fc2_dgrad")
         dh.mul_(st.act_grad)
@@ -458,15 +486,17 @@ def moe_backward_params(st: LayerState, kept, has_b1=True, has_b2=True, grad_dty
     them in place (the weight GEMMs accumulate onto their output) and they are returned."""
     r = st.routing
     dys, dh = kept
+    db1_new = (st.db1 if st.db1 is not None else ess(dh, r)) if has_b1 else None
+    st.db1 = None
     if into is None:
         dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine, tag="dw2")
         dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine, tag="dw1")
-        return dw1, dw2, (ess(dh, r) if has_b1 else None), (ess(dys, r) if has_b2 else None)
+        return dw1, dw2, db1_new, (ess(dys, r) if has_b2 else None)
     dw1, dw2, db1, db2 = into
     estmm(st.h, dys, r, out=dw2, beta=1, engine=engine, tag="dw2")
     estmm(dh, st.xs, r, out=dw1, beta=1, engine=engine, tag="dw1")
     if has_b1:
-        db1 += ess(dh, r)
+        db1 += db1_new
     if has_b2:
         db2 += ess(dys, r)
     return dw1, dw2, db1, db2
@@ -476,7 +506,7 @@ def moe_backward(st: LayerState, dy, w1, w2, act_id: int, has_b1=True, has_b2=Tr
                  engine=L.ENGINE_AUTO):
     """Gradients of moe_forward.  Returns (dx [T,d], dw1 [E,H,d], dw2 [E,H,d_out], db1 [E,H] | None,
     db2 [E,d_out] | None); bias gradients are float32, weight gradients `grad_dtype` (default: dtype of dy)."""
-    dh, dw2, db2 = moe_backward_fc2(st, dy, w2, act_id, has_b2, grad_dtype, engine)
+    dh, dw2, db2 = moe_backward_fc2(st, dy, w2, act_id, has_b2, grad_dtype, engine, want_db1=has_b1)
     dx, dw1, db1 = moe_backward_fc1(st, dh, w1, has_b1, grad_dtype, engine)
     return dx, dw1, dw2, db1, db2
 
@@ -529,8 +559,9 @@ def dense_backward(st: LayerState, dy, w1, w2, act_id: int, has_b1=True, has_b2=
     dys = _dense_rows(dy, r)
     db2 = ess(dys, r).view(-1) if has_b2 else None
     dw2 = estmm(st.h, dys, r, out_dtype=grad_dtype, engine=engine)[0]
-    dh = esmm(dys, w2.unsqueeze(0), L.B_NK, r, None, L.EPI_DACT, act_id, aux=st.y1, engine=engine)
-    db1 = ess(dh, r).view(-1) if has_b1 else None
+    dh = _hidden_gradient(st, dys, w2.unsqueeze(0), act_id, engine, has_b1)
+    db1 = (st.db1 if st.db1 is not None else ess(dh, r)).view(-1) if has_b1 else None
+    st.db1 = None
     dw1 = estmm(dh, st.xs, r, out_dtype=grad_dtype, engine=engine)[0]
     dxs = esmm(dh, w1.unsqueeze(0), L.B_KN, r, None, L.EPI_LINEAR, engine=engine)
     return dxs[:T], dw1, dw2, db1, db2

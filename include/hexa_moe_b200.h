@@ -224,6 +224,21 @@ int hexa_ess(const void* src, int64_t src_ld, const int32_t* pad_offsets, int nu
              int64_t row_capacity, int64_t cols, float* out, int64_t ldo, int dtype, void* workspace,
              size_t workspace_bytes, void* stream);
 
+/* ESMM and ESS of its output in one pass.  No counterpart as a single call: the reference computes the hidden
+ * gradient and then sums it per expert in its fused backward kernel (task 2 of launch_fused_grad_bias_*,
+ * kernels/fused.py:111-141, reading the gradient back).  Arguments up to `engine` are hexa_esmm's.  Additionally
+ * sums[e,:] (fp32 [E, n_out], ld_sums) = sum over expert e's rows of c as it was stored (after rounding to the 16-bit
+ * type), i.e. what hexa_ess(c, ...) returns up to the order of the fp32 additions.  On the tcgen05 engine the epilogue
+ * adds up every 128-row block while it is staged for its store, so c is not read again; otherwise the call runs
+ * hexa_esmm and hexa_ess one after the other.  workspace: hexa_ess_workspace_bytes(row_capacity, n_out).
+ * Deterministic (fixed order of additions). */
+int hexa_esmm_ess(const void* a, int64_t lda, const void* b, int b_layout, int64_t ldb, int64_t b_estride,
+                  const float* bias, int64_t ldbias, void* aux, int64_t ldaux, void* c, int64_t ldc,
+                  const int32_t* tile_expert, const int32_t* pad_offsets, const int32_t* row_token,
+                  const int32_t* pair_block, int num_experts, int64_t row_capacity, int64_t n_out, int64_t k,
+                  int dtype, int epilogue, int act, int engine, float* sums, int64_t ld_sums, void* workspace,
+                  size_t workspace_bytes, void* stream);
+
 /* ESS without caller-provided scratch.  No counterpart in the reference (its launchers cudaMalloc their
  * own scratch on every call, kernels/shared_cuda_core.cu:304-309).  Same result as hexa_ess, bit for bit,
  * but pass 1's partial sums live in a fixed 32 MiB array inside the library, so the call allocates nothing

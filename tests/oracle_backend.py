@@ -30,7 +30,7 @@ def _full(st, dy):
     return st.res
 
 
-def moe_backward_fc2(st, dy, w2, act_id, has_b2=True, grad_dtype=None, engine=0, ranks=1):
+def moe_backward_fc2(st, dy, w2, act_id, has_b2=True, grad_dtype=None, engine=0, ranks=1, want_db1=False):
     r = _full(st, dy)
     gd = grad_dtype or dy.dtype
     return None, r["dw2"].to(gd), (r["db2"].float() if has_b2 else None)
@@ -45,7 +45,7 @@ def moe_backward_fc1(st, dh, w1, has_b1=True, grad_dtype=None, engine=0, ranks=1
     return r["dx"].to(st.x.dtype), dw1, db1
 
 
-def moe_backward_inputs(st, dy, w1, w2, act_id, engine=0):
+def moe_backward_inputs(st, dy, w1, w2, act_id, engine=0, want_db1=False):
     r = _full(st, dy)
     return r["dx"].to(st.x.dtype), (st, dy)
 

@@ -383,6 +383,42 @@ def test_esmm_by_expert_groups_equals_one_launch(ops, dtype, n_out):
         ops.esmm(xs, w, Lb.B_NK, r, b, out=out, experts=(5, 9))
 
 
+@pytest.mark.parametrize("dtype,K,N,epilogue,b_layout", [(torch.bfloat16, 256, 512, 2, 0), (torch.float16, 256, 512, 2, 0),
+                                                          (torch.bfloat16, 512, 328, 0, 1), (torch.bfloat16, 128, 64, 1, 0),
+                                                          (torch.bfloat16, 256, 1639, 2, 0), (torch.float32, 64, 96, 0, 0)])
+def test_esmm_with_fused_column_sums(ops, dtype, K, N, epilogue, b_layout):
+    """hexa_esmm_ess: the output is bit-identical to hexa_esmm's and the sums are ESS of that output - on the tcgen05
+    engine from the epilogue's staging tile (ragged column tiles, an empty expert, both 16-bit types, all epilogues),
+    on the other engine (fp32, odd pitches) as the two-pass fallback.  Deterministic."""
+    Lb = L()
+    T, k, E = 2500, 2, 7
+    ids = make_ids(T, k, E, 11, skew=True, empty=(2,))
+    r = ops.route(ids.cuda(), E)
+    g = torch.Generator().manual_seed(3)
+    xs = ops.gather_rows(torch.randn(T, K, generator=g).to(dtype).cuda(), r)
+    w = (torch.randn(E, K, N, generator=g) / K ** 0.5).to(dtype)
+    wdev = (w.transpose(1, 2).contiguous() if b_layout == Lb.B_NK else w).cuda()
+    bias = ops._f32(torch.randn(E, N, generator=g).cuda()) if epilogue != Lb.EPI_DACT else None
+    aux = None
+    if epilogue == Lb.EPI_DACT:
+        aux = ops.gather_rows(torch.randn(T, N, generator=g).to(dtype).cuda(), r)
+    elif epilogue == Lb.EPI_ACT:
+        aux = ops.sorted_buffer(r.row_capacity, N, dtype, xs.device)
+    act = Lb.ACT_GELU if epilogue != Lb.EPI_LINEAR else Lb.ACT_NONE
+    plain = ops.esmm(xs, wdev, b_layout, r, bias, epilogue, act, aux=aux)
+    sums = torch.full((E, N), float("nan"), dtype=torch.float32, device="cuda")
+    fused = ops.esmm(xs, wdev, b_layout, r, bias, epilogue, act, aux=aux, sums=sums)
+    n_pad = int(r.pad_offsets[-1])
+    assert torch.equal(fused[:n_pad], plain[:n_pad])
+    want = ops.ess(plain, r)
+    assert torch.isfinite(sums).all()
+    assert rel_err(sums, want) < 1e-5
+    assert (sums[2] == 0).all()                                   # the empty expert
+    sums2 = torch.empty_like(sums)
+    ops.esmm(xs, wdev, b_layout, r, bias, epilogue, act, aux=aux, sums=sums2)
+    assert torch.equal(sums, sums2)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
 @pytest.mark.parametrize("n_recv", [0, 1, 2, 3, 5, 7])
 def test_mean_slices(ops, dtype, n_recv):
